@@ -469,7 +469,7 @@ __global__ void __launch_bounds__((ROWS / 32 + 3) * 32) gemm_q_kernel(const __gr
 
     if (warp < DW) {
         // ================= dequantising threads: thread <-> weight row. One instantiation per quant type keeps the
-        // loop a CTA actually runs small enough for the instruction cache (all five inlined: ~100 KB of SASS).
+        // loop a CTA actually runs small enough for the instruction cache (all five inlined make a very large loop body).
         DeqCtx cx;
         cx.sh = &sh; cx.stage0 = stage0; cx.raw0 = raw0; cx.S = S; cx.NR = NR; cx.raw_stage_bytes = raw_stage_bytes; cx.box = box;
         cx.tid = tid; cx.n = n; cx.n_sp = n_sp; cx.sp0 = sp0; cx.kb0 = kb0; cx.err = p.err; cx.a_bytes = a_bytes; cx.lbo_a = lbo_a;

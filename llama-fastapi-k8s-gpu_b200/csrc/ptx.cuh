@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers used by the sm_100a kernels: mbarrier, 1-D TMA bulk copies
-// (cp.async.bulk -> SASS UBLKCP), programmatic dependent launch, warp helpers.
+// (cp.async.bulk), programmatic dependent launch, warp helpers.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
