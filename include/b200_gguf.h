@@ -145,10 +145,18 @@ int b2_synchronize(b2_engine* e);
 #define B2_MIX_DELTA_RULE 4      /* gated delta rule: per-head matrix memory with per-row input-dependent decays, short
                                     causal convolutions on q / k / v */
 #define B2_MIX_SSD 5             /* Mamba-2 state-space recurrence: scalar decay per head, grouped B / C, gated group norm */
+#define B2_MIX_CHUNK_LINEAR 6    /* chunk-local attention with sigmoid key weights (whole-projection query / key norm, capped
+                                    scores, per-head bias, no rotation) beside a linear attention with one fixed decay per head
+                                    (SiLU feature maps, gated RMS norm over all heads); the outputs are added with fixed weights */
 #define B2_FF_RELU2 0            /* squared-ReLU block with biases (when n_ff > 0) */
 #define B2_FF_MOE 1              /* routed mixture of gated (SiLU) experts, n_ff = width of one expert */
+#define B2_FF_GLU 2              /* gated SiLU unit without biases: down(silu(gate x) * (up x)) */
+#define B2_ROUTE_SOFTMAX_ALL 0   /* scores = softmax over all slots; an additive correction steers the choice only */
+#define B2_ROUTE_TOPK_SOFTMAX 1  /* biased logits choose; weights = softmax over the chosen logits */
 #define B2_BLOCK_POSTSUM_LN 0    /* x <- LayerNorm(alpha * x + f(x)) */
 #define B2_BLOCK_PRENORM_RMS 1   /* x <- x + m * f(RMSNorm(x) * (1 + w)); the embedding and the output are normed the same way */
+#define B2_BLOCK_OUTNORM_RMS 2   /* x <- x + RMSNorm_parts(f(x)) * w: the branch OUTPUT is normed, over norm_groups equal parts;
+                                    the output norm has the same form */
 typedef struct b2_layer_desc {
     int32_t mixer;            /* B2_MIX_* */
     int32_t n_ff;             /* width of the feed-forward block (of one expert for B2_FF_MOE); 0 = the layer has none */
@@ -169,6 +177,13 @@ typedef struct b2_layer_desc {
     /* mixture of experts */
     int32_t moe_experts, moe_identity, moe_top, moe_groups, moe_keep, pad1_;
     double moe_scale;
+    int32_t moe_route;        /* B2_ROUTE_* */
+    int32_t moe_shared_ff;    /* width of a gated expert every token also runs (0: none) */
+    /* chunk-local sigmoid attention (n_head, n_head_kv, head_dim, attn_scale as above; window = chunk size, <= 0: causal over
+     * the whole sequence) beside fixed-decay linear attention (mm_heads, mm_dim, mm_vdim; decays in tensor mix.right.decay) */
+    int32_t attn_vdim, pad2_;
+    double softcap;           /* score <- softcap * tanh(score / softcap); <= 0: scores are not capped */
+    double branch_scale[2];   /* weights of the two branches in the sum */
 } b2_layer_desc;
 typedef struct b2_layered_config {
     int32_t n_layer, n_embd, n_vocab;
@@ -180,6 +195,9 @@ typedef struct b2_layered_config {
     int32_t device, flags;    /* B2_FLAG_F32 */
     int32_t block_style;      /* B2_BLOCK_* */
     float logit_scale;        /* logits = head x * logit_scale (0 is read as 1) */
+    float embed_scale;        /* the embedding row times this (0 is read as 1) */
+    int32_t norm_groups;      /* B2_BLOCK_OUTNORM_RMS: equal consecutive parts of the width, each normed by itself (0 is read as 1) */
+    int32_t tie_head;         /* != 0: the output map is the embedding table (no tensor "head") */
 } b2_layered_config;
 /* Then b2_upload_tensor for every tensor (BF16 / F32), b2_engine_finalize, b2_seq_set_blocks / b2_seq_begin (n_past must be
  * 0: recurrent state cannot be rewound; it zeroes the slot's state) as for any engine. */

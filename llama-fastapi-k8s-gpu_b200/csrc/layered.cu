@@ -1,8 +1,9 @@
 // Layer-list models (include/b200_gguf.h: b2_engine_create_layered, b2_step): the graph of a decoder given as a list of
 // layers over dense bf16 / f32 tensors, stepped over ragged batches. Token mixers: window attention beside a selective
-// scan, an mLSTM matrix memory, latent attention, the gated delta rule, a Mamba-2 state-space layer. Feed-forward blocks:
-// squared ReLU with biases, or a routed mixture of gated experts. Two block styles: layer norm AFTER each residual sum, or
-// pre-norm (zero-centred RMS weights) with a scaled branch. Shares the engine object with the llama graph (engine.cu): tensors, sequence slots and their page tables,
+// scan, an mLSTM matrix memory, latent attention, the gated delta rule, a Mamba-2 state-space layer, chunk-local sigmoid
+// attention beside fixed-decay linear attention. Feed-forward blocks: squared ReLU with biases, a gated SiLU unit, or a routed
+// mixture of gated experts (with an optional shared expert). Three block styles: layer norm AFTER each residual sum,
+// pre-norm (zero-centred RMS weights) with a scaled branch, or an RMS norm in parts on each branch's OUTPUT. Shares the engine object with the llama graph (engine.cu): tensors, sequence slots and their page tables,
 // sampler state, stream, error reporting. Owns: fused projection matrices, per-layer cache pages, per-slot recurrent
 // state, the step workspace.
 #include "engine_state.h"
@@ -51,6 +52,13 @@ struct LyLayer {
     // mixture of experts: gate_up = [E][2 ff][W] with rows 2i = gate i, 2i + 1 = up i; e_down = [E][W][ff]
     DenseW router, gate_up, e_down;
     float* correction = nullptr;
+    // gated unit (alone, or the mixture's shared expert): gate and up rows interleaved [2 ff][W], down [W][ff]
+    DenseW glu_gate_up, glu_down;
+    // chunk-local sigmoid attention + fixed-decay linear attention: cl_proj rows left q | k | v | right q | k | v | g;
+    // cl_o = [W][H * vdim + heads * vdim'] the two output maps side by side (one product forms the weighted sum)
+    DenseW cl_proj, cl_o;
+    int rq_off = 0;
+    float *pb = nullptr, *decay = nullptr, *la_state = nullptr;
 };
 
 struct StepGraph { cudaGraphExec_t exec = nullptr; int n_launch = 0; bool failed = false; };
@@ -180,12 +188,14 @@ static int concat_f32(b2_engine* e, LayeredModel* m, const std::vector<std::pair
 }
 
 // the experts of a layer stacked: [E][2 ff][W] with gate and up rows interleaved, and [E][W][ff]
-static int stack_experts(b2_engine* e, LayeredModel* m, const std::string& p, int E, int ff, int W, DenseW& gate_up, DenseW& down) {
+// (names p + "<index>."); n_experts == 0: the single unit named p + "."
+static int stack_experts(b2_engine* e, LayeredModel* m, const std::string& p, int n_experts, int ff, int W, DenseW& gate_up, DenseW& down) {
     int type = -1;
     void *gu = nullptr, *dn = nullptr;
+    const int E = std::max(1, n_experts);
     for (int x = 0; x < E; x++) {
         DevTensor tg, tu, td;
-        const std::string q = p + "e" + std::to_string(x) + ".";
+        const std::string q = n_experts > 0 ? p + std::to_string(x) + "." : p + ".";
         int rc;
         if ((rc = find(e, q + "gate", W, ff, tg)) || (rc = find(e, q + "up", W, ff, tu)) || (rc = find(e, q + "down", ff, W, td))) return rc;
         if (type < 0) {
@@ -247,11 +257,12 @@ int layered_finalize(b2_engine* e) {
     CK(cudaSetDevice(c.device));
     int rc;
     if ((rc = matrix(e, "embed", V, W, m->embed))) return rc;
-    if ((rc = matrix(e, "head", V, W, m->head))) return rc;
+    if (c.tie_head) m->head = m->embed;
+    else if ((rc = matrix(e, "head", V, W, m->head))) return rc;
     if ((rc = vec_f32(e, m, "final.norm", W, 1, &m->final_norm))) return rc;
     if (c.block_style == B2_BLOCK_PRENORM_RMS && (rc = vec_f32(e, m, "embed.norm", W, 1, &m->embed_norm))) return rc;
     const size_t cache_esz = m->exact ? 4 : 2;
-    size_t max_proj = 1, max_buf = 1, max_ff = 1, max_attn = 0, max_attn_d = 0;
+    size_t max_proj = 1, max_buf = 1, max_ff = 1, max_attn = 0, max_attn_d = 0, max_glu = 0;
     size_t moe_pairs = 0, moe_slots = 0, moe_ff = 0, moe_experts = 0, moe_xb = 0;     // moe_xb: expert activations per step token
     for (int li = 0; li < c.n_layer; li++) {
         LyLayer& L = m->layers[li];
@@ -316,6 +327,38 @@ int layered_finalize(b2_engine* e) {
             max_proj = std::max<size_t>(max_proj, L.la_proj.N);
             max_buf = std::max<size_t>({max_buf, (size_t)H * Dk, (size_t)H * dq, (size_t)vd});
             max_attn = 1; max_attn_d = std::max<size_t>(max_attn_d, d.la_rank);
+        } else if (d.mixer == B2_MIX_CHUNK_LINEAR) {
+            const std::string a = p + "mix.left.", b = p + "mix.right.";
+            const int qd = d.n_head * d.head_dim, kd = d.n_head_kv * d.head_dim, vd = d.n_head_kv * d.attn_vdim, od = d.n_head * d.attn_vdim;
+            const int rqd = d.mm_heads * d.mm_dim, rvd = d.mm_heads * d.mm_vdim;
+            std::vector<int> offs;
+            if ((rc = fuse(e, m, {{a + "q", qd}, {a + "k", kd}, {a + "v", vd}, {b + "q", rqd}, {b + "k", rqd}, {b + "v", rvd}, {b + "g", rvd}}, W,
+                           L.cl_proj, offs))) return rc;
+            L.q_off = offs[0]; L.k_off = offs[1]; L.v_off = offs[2]; L.rq_off = offs[3]; L.g_off = offs[6];
+            if ((rc = vec_f32(e, m, a + "q.norm", qd, 1, &L.q_norm))) return rc;
+            if ((rc = vec_f32(e, m, a + "k.norm", kd, 1, &L.k_norm))) return rc;
+            if ((rc = vec_f32(e, m, a + "pb", d.n_head, 1, &L.pb))) return rc;
+            if ((rc = vec_f32(e, m, b + "norm", rvd, 1, &L.mm_norm))) return rc;
+            if ((rc = vec_f32(e, m, b + "decay", d.mm_heads, 1, &L.decay))) return rc;
+            {   // the two output maps side by side: [W][od + rvd]
+                DevTensor tl, tr;
+                if ((rc = find(e, a + "o", od, W, tl)) || (rc = find(e, b + "o", rvd, W, tr))) return rc;
+                if (tl.type != tr.type) return b2_fail(B2_ERR_UNSUPPORTED, a + "o: the two output maps must share a dtype");
+                const size_t esz = tl.type == T_BF16 ? 2 : 4, Kt = (size_t)od + rvd;
+                void* cat = nullptr;
+                if ((rc = dev_alloc(m, &cat, (size_t)W * Kt * esz + 64))) return rc;
+                CK(cudaMemcpy2DAsync(cat, Kt * esz, tl.ptr, od * esz, od * esz, W, cudaMemcpyDeviceToDevice, e->stream));
+                CK(cudaMemcpy2DAsync((char*)cat + od * esz, Kt * esz, tr.ptr, rvd * esz, rvd * esz, W, cudaMemcpyDeviceToDevice, e->stream));
+                L.cl_o.w = cat; L.cl_o.type = tl.type; L.cl_o.N = W; L.cl_o.K = (int)Kt;
+            }
+            const size_t kpool = (size_t)c.kv_num_blocks * d.n_head_kv * c.kv_block_tokens * d.head_dim * cache_esz;
+            const size_t vpool = (size_t)c.kv_num_blocks * d.n_head_kv * c.kv_block_tokens * d.attn_vdim * cache_esz;
+            if ((rc = dev_alloc(m, &L.k_pool, kpool, true))) return rc;
+            if ((rc = dev_alloc(m, &L.v_pool, vpool, true))) return rc;
+            e->kv_bytes += (int64_t)(kpool + vpool);
+            if ((rc = dev_alloc(m, (void**)&L.la_state, (size_t)S * col_state_floats(d.mm_heads, d.mm_dim, d.mm_vdim) * 4, true))) return rc;
+            max_proj = std::max<size_t>(max_proj, L.cl_proj.N);
+            max_buf = std::max<size_t>({max_buf, (size_t)qd, (size_t)od + rvd});
         } else if (d.mixer == B2_MIX_DELTA_RULE) {
             const std::string a = p + "mix.";
             const int H = d.mm_heads, G = d.key_heads, kd = G * d.mm_dim, vd = H * d.mm_vdim;
@@ -379,13 +422,21 @@ int layered_finalize(b2_engine* e) {
             const int slots = d.moe_experts + d.moe_identity;
             if ((rc = vec_f32(e, m, p + "norm2", W, 1, &L.norm2))) return rc;
             if ((rc = matrix(e, p + "mlp.router", slots, W, L.router))) return rc;
-            if ((rc = vec_f32(e, m, p + "mlp.correction", slots, 1, &L.correction))) return rc;
-            if ((rc = stack_experts(e, m, p + "mlp.", d.moe_experts, d.n_ff, W, L.gate_up, L.e_down))) return rc;
+            if ((rc = vec_f32(e, m, p + (d.moe_route == B2_ROUTE_TOPK_SOFTMAX ? "mlp.router.b" : "mlp.correction"), slots, 1, &L.correction))) return rc;
+            if ((rc = stack_experts(e, m, p + "mlp.e", d.moe_experts, d.n_ff, W, L.gate_up, L.e_down))) return rc;
+            if (d.moe_shared_ff > 0) {
+                if ((rc = stack_experts(e, m, p + "mlp.shared", 0, d.moe_shared_ff, W, L.glu_gate_up, L.glu_down))) return rc;
+                max_glu = std::max<size_t>(max_glu, d.moe_shared_ff);
+            }
             moe_pairs = std::max<size_t>(moe_pairs, (size_t)Tm * d.moe_top);
             moe_slots = std::max<size_t>(moe_slots, slots);
             moe_ff = std::max<size_t>(moe_ff, d.n_ff);
             moe_xb = std::max<size_t>(moe_xb, (size_t)d.moe_top * d.n_ff);
             moe_experts = std::max<size_t>(moe_experts, d.moe_experts);
+        } else if (d.n_ff > 0 && d.ff_kind == B2_FF_GLU) {
+            if ((rc = vec_f32(e, m, p + "norm2", W, 1, &L.norm2))) return rc;
+            if ((rc = stack_experts(e, m, p + "mlp", 0, d.n_ff, W, L.glu_gate_up, L.glu_down))) return rc;
+            max_glu = std::max<size_t>(max_glu, d.n_ff);
         } else if (d.n_ff > 0) {
             if ((rc = vec_f32(e, m, p + "norm2", W, 1, &L.norm2))) return rc;
             if ((rc = matrix(e, p + "mlp.up", d.n_ff, W, L.up))) return rc;
@@ -401,6 +452,7 @@ int layered_finalize(b2_engine* e) {
     if ((rc = dev_alloc(m, (void**)&m->oL, (size_t)Tm * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->oR, (size_t)Tm * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->hn, (size_t)Tm * W * 4))) return rc;
+    max_ff = std::max(max_ff, max_glu);
     if ((rc = dev_alloc(m, (void**)&m->ff, (size_t)Tm * max_ff * 4))) return rc;
     if (!m->exact && (rc = dev_alloc(m, (void**)&m->xb, (size_t)(Tm + B2_STEP_MAX_ENTRIES) * std::max<size_t>({max_buf, max_ff, (size_t)W, moe_xb}) * 2 + 64))) return rc;
     if (max_attn > 0) {
@@ -459,6 +511,9 @@ int layered_seq_reset(b2_engine* e, int slot) {
             CK(cudaMemsetAsync(L.ssm_state + slot * ss, 0, ss * 4, e->stream));
         } else if (d.mixer == B2_MIX_LATENT_ATTN) {
             // nothing but cache pages, which are overwritten
+        } else if (d.mixer == B2_MIX_CHUNK_LINEAR) {
+            const size_t ss = col_state_floats(d.mm_heads, d.mm_dim, d.mm_vdim);
+            CK(cudaMemsetAsync(L.la_state + slot * ss, 0, ss * 4, e->stream));
         } else if (d.mixer == B2_MIX_DELTA_RULE || d.mixer == B2_MIX_SSD) {
             const size_t cs = (size_t)std::max(1, d.conv_taps - 1) * L.conv_C;
             const size_t ss = col_state_floats(d.mm_heads, d.mixer == B2_MIX_SSD ? d.d_state : d.mm_dim, d.mm_vdim);
@@ -511,6 +566,11 @@ extern "C" int b2_engine_create_layered(const b2_layered_config* c, const b2_lay
                 d.norm_groups <= 0 || (d.mm_heads * d.mm_vdim) % d.norm_groups)
                 return b2_fail(B2_ERR_ARG, li + "bad state-space sizes");
             if (d.d_state > 256) return b2_fail(B2_ERR_UNSUPPORTED, li + "state size above 256");
+        } else if (d.mixer == B2_MIX_CHUNK_LINEAR) {
+            if (d.n_head <= 0 || d.n_head_kv <= 0 || d.n_head % d.n_head_kv || d.head_dim <= 0 || d.attn_vdim <= 0) return b2_fail(B2_ERR_ARG, li + "bad head counts");
+            if (d.head_dim > 256 || d.attn_vdim > 256) return b2_fail(B2_ERR_UNSUPPORTED, li + "key or value size above 256");
+            if (d.mm_heads <= 0 || d.mm_dim <= 0 || d.mm_vdim <= 0) return b2_fail(B2_ERR_ARG, li + "bad linear-attention sizes");
+            if (d.mm_dim > 256) return b2_fail(B2_ERR_UNSUPPORTED, li + "linear-attention key size above 256");
         } else return b2_fail(B2_ERR_UNSUPPORTED, li + "unknown mixer kind");
         if (d.n_ff > 0 && d.ff_kind == B2_FF_MOE) {
             const int slots = d.moe_experts + d.moe_identity;
@@ -518,11 +578,17 @@ extern "C" int b2_engine_create_layered(const b2_layered_config* c, const b2_lay
                 d.moe_keep <= 0 || d.moe_keep > d.moe_groups || d.moe_top > d.moe_keep * (slots / d.moe_groups))
                 return b2_fail(B2_ERR_ARG, li + "bad mixture-of-experts sizes");
             if (slots > 4096) return b2_fail(B2_ERR_UNSUPPORTED, li + "more than 4096 expert slots");
-        } else if (d.ff_kind != B2_FF_RELU2) return b2_fail(B2_ERR_UNSUPPORTED, li + "unknown feed-forward kind");
+            if (d.moe_route != B2_ROUTE_SOFTMAX_ALL && d.moe_route != B2_ROUTE_TOPK_SOFTMAX) return b2_fail(B2_ERR_ARG, li + "unknown routing rule");
+            if (d.moe_route == B2_ROUTE_TOPK_SOFTMAX && (d.moe_identity > 0 || d.moe_groups > 1)) return b2_fail(B2_ERR_UNSUPPORTED, li + "top-k softmax routing has no identity slots or groups");
+            if (d.moe_shared_ff < 0) return b2_fail(B2_ERR_ARG, li + "negative shared-expert width");
+        } else if (d.ff_kind != B2_FF_RELU2 && d.ff_kind != B2_FF_GLU) return b2_fail(B2_ERR_UNSUPPORTED, li + "unknown feed-forward kind");
         if (c->block_style == B2_BLOCK_PRENORM_RMS ? (d.mixer == B2_MIX_WINDOW_SCAN) : false)
             return b2_fail(B2_ERR_UNSUPPORTED, li + "the two-branch mixer belongs to post-sum blocks");
     }
-    if (c->block_style != B2_BLOCK_POSTSUM_LN && c->block_style != B2_BLOCK_PRENORM_RMS) return b2_fail(B2_ERR_ARG, "unknown block style");
+    if (c->block_style != B2_BLOCK_POSTSUM_LN && c->block_style != B2_BLOCK_PRENORM_RMS && c->block_style != B2_BLOCK_OUTNORM_RMS)
+        return b2_fail(B2_ERR_ARG, "unknown block style");
+    if (c->block_style == B2_BLOCK_OUTNORM_RMS && (c->norm_groups < 0 || (c->norm_groups > 0 && c->n_embd % c->norm_groups)))
+        return b2_fail(B2_ERR_ARG, "the norm's parts must divide the width");
     b2_engine* e = new b2_engine();
     b2_config& b = e->cfg;
     memset(&b, 0, sizeof(b));
@@ -772,12 +838,58 @@ static int mix_ssd(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r
     return dense(e, m, L.st_o, m->buf[2], inner, m->oL, W, T);
 }
 
+// both branches read `in`; the weighted sum of their outputs is formed by ONE product over [left heads | right heads]
+static int mix_chunk_linear(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const b2_layered_config& c = m->c;
+    const b2_layer_desc& d = L.d;
+    cudaStream_t st = e->stream;
+    const int T = r.T, W = c.n_embd, Np = L.cl_proj.N;
+    const int od = d.n_head * d.attn_vdim, rqd = d.mm_heads * d.mm_dim, rvd = d.mm_heads * d.mm_vdim, Kt = od + rvd;
+    int rc;
+    if ((rc = dense(e, m, L.cl_proj, in, W, m->proj, Np, T))) return rc;
+    SigmoidAttnArgs a = {};
+    a.proj = m->proj; a.ldp = Np; a.q_off = L.q_off; a.k_off = L.k_off; a.v_off = L.v_off; a.q_norm_w = L.q_norm; a.k_norm_w = L.k_norm;
+    a.k_pool = L.k_pool; a.v_pool = L.v_pool; a.cache_f32 = m->exact ? 1 : 0; a.block_tables = m->block_tables; a.block_tokens = c.kv_block_tokens;
+    a.H = d.n_head; a.G = d.n_head_kv; a.d = d.head_dim; a.dv = d.attn_vdim; a.chunk = d.window;
+    a.scale = (float)d.attn_scale; a.softcap = (float)d.softcap; a.eps = c.norm_eps; a.bias = L.pb;
+    a.q_out = m->buf[0]; a.out = m->buf[1]; a.ld_out = Kt; a.out_scale = (float)d.branch_scale[0];
+    a.act = m->proj + L.rq_off; a.act_n = 2 * rqd + rvd;          // the linear branch's q | k | v get their SiLU in the same pass
+    {
+        StepProfiler sp(m, st, 2);
+        CK(sigmoid_attn_store_launch(a, r, st));
+        CK(sigmoid_attn_launch(a, r, st));
+        e->launches += 2;
+    }
+    ColStateArgs cs = {};
+    cs.wk = m->proj + L.rq_off + rqd; cs.ld_wk = Np; cs.rk = m->proj + L.rq_off; cs.ld_rk = Np;
+    cs.head_const = L.decay; cs.val = m->proj + L.rq_off + 2 * rqd; cs.ld_v = Np;
+    cs.H = d.mm_heads; cs.G = d.mm_heads; cs.R = d.mm_dim; cs.P = d.mm_vdim; cs.delta = 0;
+    cs.state = L.la_state; cs.y = m->buf[2]; cs.ld_y = rvd;
+    GroupNormArgs gn = {};
+    gn.x = m->buf[2]; gn.ld_x = rvd; gn.gate = m->proj + L.g_off; gn.ld_g = Np; gn.w = L.mm_norm; gn.w_gstride = 0; gn.groups = 1; gn.n = rvd;
+    gn.eps = c.norm_eps; gn.gate_first = 0; gn.y = m->buf[1] + od; gn.ld_y = Kt; gn.out_scale = (float)d.branch_scale[1];
+    {
+        StepProfiler sp(m, st, 4);
+        CK(col_state_launch(cs, r, st));
+        CK(group_norm_gate_launch(gn, T, st));
+        e->launches += 2;
+    }
+    return dense(e, m, L.cl_o, m->buf[1], Kt, m->oL, W, T);
+}
+
 // ---- feed-forward blocks: input `in` [T][W], output in m->oL
 static int ff_relu2(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
     const int T = r.T, W = m->c.n_embd;
     int rc;
     if ((rc = dense(e, m, L.up, in, W, m->ff, L.d.n_ff, T, L.up_b, EPI_BIAS_RELU2))) return rc;
     return dense(e, m, L.down, m->ff, L.d.n_ff, m->oL, W, T, L.down_b, EPI_BIAS);
+}
+
+static int ff_glu(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const int T = r.T, W = m->c.n_embd, ff = L.glu_down.K;
+    int rc;
+    if ((rc = dense(e, m, L.glu_gate_up, in, W, m->ff, ff, T, nullptr, EPI_GLU_SILU))) return rc;
+    return dense(e, m, L.glu_down, m->ff, ff, m->oL, W, T);
 }
 
 // defer != nullptr: the weighted sum of the expert outputs is left to the caller's residual kernel (described in *defer)
@@ -792,6 +904,7 @@ static int ff_moe(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r,
     MoeRouteArgs ra = {};
     ra.logits = m->moe_logits; ra.ld = slots; ra.correction = L.correction; ra.n_slots = slots; ra.n_experts = d.moe_experts;
     ra.top = d.moe_top; ra.n_groups = d.moe_groups; ra.keep_groups = d.moe_keep; ra.scale = (float)d.moe_scale;
+    ra.mode = d.moe_route == B2_ROUTE_TOPK_SOFTMAX ? 1 : 0;
     ra.sel = m->moe_sel; ra.weight = m->moe_weight; ra.pair_token = m->moe_tok;
     DenseGroups g = {};
     g.n_groups = d.moe_experts;
@@ -841,11 +954,13 @@ static int run_mixer(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev&
         case B2_MIX_LATENT_ATTN: return mix_latent_attn(e, m, L, r, in);
         case B2_MIX_DELTA_RULE: return mix_delta_rule(e, m, L, r, in);
         case B2_MIX_SSD: return mix_ssd(e, m, L, r, in);
+        case B2_MIX_CHUNK_LINEAR: return mix_chunk_linear(e, m, L, r, in);
     }
     return b2_fail(B2_ERR_UNSUPPORTED, "unknown mixer kind");
 }
 static int run_ff(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in, MoeJoinArgs* defer = nullptr) {
-    return L.d.ff_kind == B2_FF_MOE ? ff_moe(e, m, L, r, in, defer) : ff_relu2(e, m, L, r, in);
+    if (L.d.ff_kind == B2_FF_MOE) return ff_moe(e, m, L, r, in, defer);
+    return L.d.ff_kind == B2_FF_GLU ? ff_glu(e, m, L, r, in) : ff_relu2(e, m, L, r, in);
 }
 
 static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
@@ -856,7 +971,7 @@ static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
     int rc;
     {
         StepProfiler sp(m, st, 0);
-        CK(embed_ragged_launch(m->embed.w, m->embed.type, W, r.tok_id, T, m->x, st));
+        CK(embed_ragged_launch(m->embed.w, m->embed.type, W, r.tok_id, T, m->x, c.embed_scale != 0.f ? c.embed_scale : 1.f, st));
         e->launches++;
         if (prenorm) {
             CK(resid_rms_norm_launch(m->x, nullptr, 0.f, m->embed_norm, 1.f, 1.f, c.norm_eps, W, T, m->x, st));
@@ -879,7 +994,29 @@ static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
     for (int li = 0; li < c.n_layer; li++) {
         LyLayer& L = m->layers[li];
         const b2_layer_desc& d = L.d;
-        if (prenorm) {
+        if (c.block_style == B2_BLOCK_OUTNORM_RMS) {
+            // both sublayers read the stream itself; what they return is normed in parts and added
+            const int ng = std::max(1, c.norm_groups);
+            if ((rc = run_mixer(e, m, L, r, m->x))) return rc;
+            {
+                StepProfiler sp(m, st, 5);
+                CK(outnorm_join_launch(m->x, m->oL, nullptr, L.norm1, ng, c.norm_eps, W, T, nullptr, st));
+                e->launches++;
+            }
+            if (d.n_ff > 0) {
+                const bool moe = d.ff_kind == B2_FF_MOE;
+                MoeJoinArgs mj = {};
+                if ((rc = run_ff(e, m, L, r, m->x, moe ? &mj : nullptr))) return rc;
+                const float* dense_part = moe ? nullptr : m->oL;
+                if (moe && d.moe_shared_ff > 0) {          // the shared expert runs for every token; the join adds it to the weighted sum
+                    if ((rc = ff_glu(e, m, L, r, m->x))) return rc;
+                    dense_part = m->oL;
+                }
+                StepProfiler sp(m, st, 5);
+                CK(outnorm_join_launch(m->x, dense_part, moe ? &mj : nullptr, L.norm2, ng, c.norm_eps, W, T, nullptr, st));
+                e->launches++;
+            }
+        } else if (prenorm) {
             if ((rc = join(L.norm1, m->hn))) return rc;
             if ((rc = run_mixer(e, m, L, r, m->hn))) return rc;
             pending = m->oL;
@@ -981,7 +1118,8 @@ extern "C" int b2_step(b2_engine* e, int n_entries, const int32_t* slots, const 
         {
             StepProfiler sp(m, st, 5);
             CK(gather_rows_launch(m->x, W, d_rows + r0, nr, m->rows, st));
-            if (c.block_style == B2_BLOCK_PRENORM_RMS) CK(resid_rms_norm_launch(m->rows, nullptr, 0.f, m->final_norm, 1.f, 1.f, c.norm_eps, W, nr, m->rows, st));
+            if (c.block_style == B2_BLOCK_OUTNORM_RMS) CK(outnorm_join_launch(nullptr, m->rows, nullptr, m->final_norm, std::max(1, c.norm_groups), c.norm_eps, W, nr, m->rows, st));
+            else if (c.block_style == B2_BLOCK_PRENORM_RMS) CK(resid_rms_norm_launch(m->rows, nullptr, 0.f, m->final_norm, 1.f, 1.f, c.norm_eps, W, nr, m->rows, st));
             else CK(layer_norm_launch(m->rows, m->final_norm, c.norm_eps, W, nr, m->rows, st));
             e->launches += 2;
         }

@@ -69,7 +69,8 @@ struct DenseArgs {
 cudaError_t dense_launch(const DenseArgs& a, cudaStream_t s);
 
 // ---------------------------------------------------------------- mixers and norms (mixers.cu)
-cudaError_t embed_ragged_launch(const void* table, int w_type, int W, const int* tok_id, int T, float* x, cudaStream_t s);
+// x[t] = table[tok_id[t]] * scale
+cudaError_t embed_ragged_launch(const void* table, int w_type, int W, const int* tok_id, int T, float* x, float scale, cudaStream_t s);
 // gather rows: y[i] = x[rows[i]]
 cudaError_t gather_rows_launch(const float* x, int W, const int* rows, int n, float* y, cudaStream_t s);
 
@@ -155,14 +156,16 @@ cudaError_t causal_conv_advance_launch(const ConvArgs& a, const RaggedDev& r, cu
 //   S[r][:] *= row_decay[r] * head_decay          (either may be absent)
 //   u = val_scale * (val - (delta ? S^T wk : 0))  (delta rule: write only what the memory does not return yet)
 //   S += wk u^T ;  y = S^T rk + skip * val        (the read-out sees the current token's write)
-// Covers the gated delta rule (row decays, delta = 1) and the Mamba-2 state-space recurrence (head decay, skip).
+// Covers the gated delta rule (row decays, delta = 1), the Mamba-2 state-space recurrence (head decay, skip) and linear
+// attention with one fixed decay per head (head_const, no value scale).
 struct ColStateArgs {
     const float* wk; int ld_wk;            // [T][G * R] write keys
     const float* rk; int ld_rk;            // [T][G * R] read keys
     const float* row_decay; int ld_rd;     // [T][H * R] or null
     const float* head_decay; int ld_hd;    // [T][H] or null
+    const float* head_const = nullptr;     // [H] or null: a decay that does not depend on the token (used when head_decay is null)
     const float* val; int ld_v;            // [T][H * P]
-    const float* val_scale; int ld_vs;     // [T][H]
+    const float* val_scale; int ld_vs;     // [T][H], or null for 1
     const float* skip;                     // [H] or null
     int H, G, R, P, delta;
     float* state;                          // [slot][H][P][Rp], Rp = R rounded up to 4 (column-major, pads stay zero)
@@ -188,6 +191,7 @@ cudaError_t ssd_prepare_launch(float* dt, int ld_dt, const float* dt_bias, const
 struct GroupNormArgs {
     const float* x; int ld_x; const float* gate; int ld_g; const float* w; int w_gstride;
     int groups, n; float eps; int gate_first;
+    float out_scale = 1.f;
     float* y; int ld_y;
 };
 cudaError_t group_norm_gate_launch(const GroupNormArgs& a, int T, cudaStream_t s);
@@ -221,6 +225,8 @@ struct MoeRouteArgs {
     const float* correction;               // [n_slots]
     int n_slots, n_experts, top, n_groups, keep_groups;
     float scale;
+    int mode = 0;                          // 0: weight = softmax over all slots (times scale), `correction` added for the choice only;
+                                           // 1: logits + correction choose, weight = softmax over the chosen biased logits
     int* sel; float* weight;               // [T][top]
     int* pair_token;                       // [T][top]: t (the input row of each pair)
 };
@@ -244,6 +250,34 @@ struct MoeJoinArgs {
 };
 cudaError_t moe_join_launch(const MoeJoinArgs& j, float* x, float mult, const float* w, float w_offset, float eps, int W, int T, float* y,
                             cudaStream_t s);
+
+// Blocks that norm what a branch RETURNS: v[t] = a[t] (if given) + the mixture's weighted sum (if given); each of `groups` equal
+// consecutive parts of v is brought to unit RMS, the whole is multiplied by w; then x[t] += that (x given) or y[t] = that.
+// y may be a.
+cudaError_t outnorm_join_launch(float* x, const float* a, const MoeJoinArgs* moe, const float* w, int groups, float eps, int W, int T,
+                                float* y, cudaStream_t s);
+
+// ---------------------------------------------------------------- sigmoid attention (sigmoid_attn.cu)
+// Attention without a softmax: the weight of a visible key is sigmoid(cap(q . k * scale) + bias[h]), cap(z) = softcap *
+// tanh(z / softcap); nothing is normalised over the keys and no position is rotated in. Visible keys: those of the query's own
+// chunk of `chunk` positions (chunks counted from position 0 of the sequence) up to the query; chunk <= 0: all earlier keys.
+// Queries and keys are RMS-normed over the WHOLE projection (all heads at once) with a weight of that size. Grouped query
+// heads; the value size may differ from the key size.
+struct SigmoidAttnArgs {
+    const float* proj; int ldp; int q_off, k_off, v_off;      // projection rows: q [H*d], k [G*d], v [G*dv]
+    const float* q_norm_w; const float* k_norm_w;              // [H*d], [G*d]
+    void* k_pool; void* v_pool; int cache_f32;                 // pages [page][G][block_tokens][d] and [page][G][block_tokens][dv]
+    int* const* block_tables; int block_tokens;
+    int H, G, d, dv, chunk;
+    float scale, softcap, eps;                                 // softcap <= 0: none
+    const float* bias;                                         // [H] or null
+    float* q_out;                                              // scratch [T][H*d]: normed queries
+    float* out; int ld_out; float out_scale;                   // out[t][h*dv + i], times out_scale
+    float* act; int act_n;                                     // act_n > 0: columns [0, act_n) of act (row stride ldp) get SiLU in place
+};
+// norm of q and k, keys and values into the pages (and the SiLU columns)
+cudaError_t sigmoid_attn_store_launch(const SigmoidAttnArgs& a, const RaggedDev& r, cudaStream_t s);
+cudaError_t sigmoid_attn_launch(const SigmoidAttnArgs& a, const RaggedDev& r, cudaStream_t s);
 
 // ---------------------------------------------------------------- graph (layered.cu)
 struct LayeredModel;

@@ -43,19 +43,19 @@ __device__ __forceinline__ float log_sigmoid_f(float z) { return -softplus_f(-z)
 
 // ---------------------------------------------------------------- embedding, gather
 template <typename TW>
-__global__ void embed_ragged_kernel(const TW* __restrict__ table, int W, const int* __restrict__ tok, float* __restrict__ x) {
+__global__ void embed_ragged_kernel(const TW* __restrict__ table, int W, const int* __restrict__ tok, float* __restrict__ x, float scale) {
     griddep_launch();
     griddep_wait();
     const int t = blockIdx.x;
     const TW* row = table + (size_t)tok[t] * W;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        if constexpr (sizeof(TW) == 2) x[(size_t)t * W + i] = __bfloat162float(row[i]);
-        else x[(size_t)t * W + i] = row[i];
+        if constexpr (sizeof(TW) == 2) x[(size_t)t * W + i] = __bfloat162float(row[i]) * scale;
+        else x[(size_t)t * W + i] = row[i] * scale;
     }
 }
-cudaError_t embed_ragged_launch(const void* table, int w_type, int W, const int* tok_id, int T, float* x, cudaStream_t s) {
-    if (w_type == T_BF16) return launch_chain(embed_ragged_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, s, (const __nv_bfloat16*)table, W, tok_id, x);
-    if (w_type == T_F32) return launch_chain(embed_ragged_kernel<float>, dim3(T), dim3(128), 0, s, (const float*)table, W, tok_id, x);
+cudaError_t embed_ragged_launch(const void* table, int w_type, int W, const int* tok_id, int T, float* x, float scale, cudaStream_t s) {
+    if (w_type == T_BF16) return launch_chain(embed_ragged_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, s, (const __nv_bfloat16*)table, W, tok_id, x, scale);
+    if (w_type == T_F32) return launch_chain(embed_ragged_kernel<float>, dim3(T), dim3(128), 0, s, (const float*)table, W, tok_id, x, scale);
     return cudaErrorInvalidValue;
 }
 

@@ -1,5 +1,5 @@
 // Mixture of experts for the layer-list models: routing (softmax scores, additive choice correction, group-limited
-// top-k with identity slots), the bookkeeping that sorts a step's (token, choice) pairs by expert into row tiles for the
+// top-k with identity slots; or biased logits with a softmax over the chosen ones), the bookkeeping that sorts a step's (token, choice) pairs by expert into row tiles for the
 // grouped products of dense.cu, and the weighted combination. Routing arithmetic is 32-bit.
 #include "kernels.h"
 #include "layered.h"
@@ -74,7 +74,43 @@ __global__ void __launch_bounds__(32) moe_route_kernel(MoeRouteArgs a) {
         __syncwarp();
     }
 }
+// grid (T), one warp: the `top` largest of logit + bias (ties to the lower index); weights = softmax over those alone.
+// shared: biased logits [n_slots], chosen values [top]
+__global__ void __launch_bounds__(32) moe_route_topk_kernel(MoeRouteArgs a) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ float rs[];
+    float* choice = rs;
+    float* picked = rs + a.n_slots;
+    const int t = blockIdx.x, lane = threadIdx.x, n = a.n_slots;
+    const float* z = a.logits + (size_t)t * a.ld;
+    for (int i = lane; i < n; i += 32) choice[i] = z[i] + (a.correction ? a.correction[i] : 0.f);
+    __syncwarp();
+    for (int k = 0; k < a.top; k++) {
+        float v = -INFINITY; int idx = 0x7fffffff;
+        for (int i = lane; i < n; i += 32) { const float c = choice[i]; if (c > v || (c == v && i < idx)) { v = c; idx = i; } }
+        warp_argmax(v, idx);
+        if (idx >= n) { idx = 0; v = -INFINITY; }
+        __syncwarp();
+        if (lane == 0) {
+            a.sel[(size_t)t * a.top + k] = idx;
+            a.pair_token[(size_t)t * a.top + k] = t;
+            picked[k] = v;
+            choice[idx] = NAN;                     // taken: NaN never wins a comparison
+        }
+        __syncwarp();
+    }
+    const float mx = picked[0];                    // the first pick is the largest
+    float sum = 0.f;
+    for (int k = 0; k < a.top; k++) sum += expf(picked[k] - mx);       // every lane the same sum, in pick order
+    for (int k = lane; k < a.top; k += 32) a.weight[(size_t)t * a.top + k] = expf(picked[k] - mx) / sum * a.scale;
+}
 cudaError_t moe_route_launch(const MoeRouteArgs& a, int T, cudaStream_t s) {
+    if (a.mode == 1) {
+        const size_t smem = (size_t)(a.n_slots + a.top) * 4;
+        if (smem > 48 * 1024) return cudaErrorInvalidValue;
+        return launch_chain(moe_route_topk_kernel, dim3(T), dim3(32), smem, s, a);
+    }
     const size_t smem = (size_t)(2 * a.n_slots + a.n_groups + 1) * 4;
     if (smem > 48 * 1024) return cudaErrorInvalidValue;
     return launch_chain(moe_route_kernel, dim3(T), dim3(32), smem, s, a);
@@ -183,6 +219,50 @@ __global__ void __launch_bounds__(256) moe_join_kernel(MoeJoinArgs j, float* __r
 cudaError_t moe_join_launch(const MoeJoinArgs& j, float* x, float mult, const float* w, float w_offset, float eps, int W, int T, float* y,
                             cudaStream_t s) {
     return launch_chain(moe_join_kernel, dim3(T), dim3(256), (size_t)W * 4, s, j, x, mult, w, w_offset, eps, W, y);
+}
+
+// grid (T): the branch output (a dense branch and / or a mixture's weighted sum) lives in shared memory between the sums of
+// squares of its parts and the scaling
+struct OutNormMoe { MoeJoinArgs j; int on; };
+__global__ void __launch_bounds__(256) outnorm_join_kernel(float* __restrict__ x, const float* __restrict__ a, OutNormMoe mo,
+                                                          const float* __restrict__ w, int groups, float eps, int W, float* __restrict__ y) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ float row[];             // [W] values, then [groups] 1 / rms
+    float* rinv = row + W;
+    const int t = blockIdx.x, n = W / groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const size_t base = (size_t)t * W;
+    const MoeJoinArgs& j = mo.j;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float acc = a ? a[base + i] : 0.f;
+        if (mo.on)
+            for (int c = 0; c < j.top; c++) {
+                const int p = t * j.top + c, e = j.sel[p];
+                const float v = e < j.n_experts ? j.rows[(size_t)(j.pos ? j.pos[p] : p) * W + i] : j.h[base + i];
+                acc = fmaf(j.weight[p], v, acc);
+            }
+        row[i] = acc;
+    }
+    __syncthreads();
+    for (int g = warp; g < groups; g += nw) {
+        float ss = 0.f;
+        for (int i = lane; i < n; i += 32) { const float v = row[g * n + i]; ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        if (lane == 0) rinv[g] = 1.f / sqrtf(ss / (float)n + eps);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = row[i] * rinv[i / n] * w[i];
+        if (x) x[base + i] += v;
+        else y[base + i] = v;
+    }
+}
+cudaError_t outnorm_join_launch(float* x, const float* a, const MoeJoinArgs* moe, const float* w, int groups, float eps, int W, int T,
+                                float* y, cudaStream_t s) {
+    if (groups <= 0 || W % groups) return cudaErrorInvalidValue;
+    OutNormMoe mo = {};
+    if (moe) { mo.j = *moe; mo.on = 1; }
+    return launch_chain(outnorm_join_kernel, dim3(T), dim3(256), (size_t)(W + groups) * 4, s, x, a, mo, w, groups, eps, W, y);
 }
 
 }  // namespace b2

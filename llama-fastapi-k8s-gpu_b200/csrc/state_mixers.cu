@@ -162,11 +162,12 @@ __global__ void __launch_bounds__(CS_WARPS * 32) col_state_kernel(ColStateArgs a
             const int u = j / CS_COLS, e = j % CS_COLS;
             const size_t t = start + i0 + u;
             if (c0 + e < P) cp_async_4(vs + (buf * CS_TB + u) * CS_COLS + e, a.val + t * a.ld_v + (size_t)h * P + c0 + e);
-            if (e == 0) cp_async_4(sc + (buf * CS_TB + u) * 2, a.val_scale + t * a.ld_vs + h);
+            if (e == 0 && a.val_scale) cp_async_4(sc + (buf * CS_TB + u) * 2, a.val_scale + t * a.ld_vs + h);
             if (e == 1 && a.head_decay) cp_async_4(sc + (buf * CS_TB + u) * 2 + 1, a.head_decay + t * a.ld_hd + h);
         }
     };
     const float skip = a.skip ? a.skip[h] : 0.f;
+    const float hconst = a.head_const ? a.head_const[h] : 1.f;
     if (len > 0) stage(0, 0);
     cp_async_commit();
     for (int i0 = 0; i0 < len; i0 += CS_TB) {
@@ -183,8 +184,8 @@ __global__ void __launch_bounds__(CS_WARPS * 32) col_state_kernel(ColStateArgs a
             float v[CS_CPL];
 #pragma unroll
             for (int j = 0; j < CS_CPL; j++) v[j] = vs[bu * CS_COLS + lc + j];
-            const float vscale = sc[bu * 2];
-            const float hd = a.head_decay ? sc[bu * 2 + 1] : 1.f;
+            const float vscale = a.val_scale ? sc[bu * 2] : 1.f;
+            const float hd = a.head_decay ? sc[bu * 2 + 1] : hconst;
             float4 kw[NCH];
             float pred[CS_CPL];
 #pragma unroll
@@ -301,7 +302,7 @@ __global__ void __launch_bounds__(128) group_norm_gate_kernel(GroupNormArgs a) {
     const float* w = a.w + (size_t)g * a.w_gstride;
     float* y = a.y + (size_t)t * a.ld_y + (size_t)g * n;
     for (int i = threadIdx.x; i < n; i += blockDim.x)
-        y[i] = a.gate_first ? x[i] * silu_f(gate[i]) * rinv * w[i] : x[i] * rinv * w[i] * sigmoid_f(gate[i]);
+        y[i] = (a.gate_first ? x[i] * silu_f(gate[i]) * rinv * w[i] : x[i] * rinv * w[i] * sigmoid_f(gate[i])) * a.out_scale;
 }
 cudaError_t group_norm_gate_launch(const GroupNormArgs& a, int T, cudaStream_t s) {
     return launch_chain(group_norm_gate_kernel, dim3(T, a.groups), dim3(128), 0, s, a);

@@ -30,6 +30,9 @@ class LayeredDims:
     n_ctx_train: int = 0
     block_style: int = _cabi.B2_BLOCK_POSTSUM_LN
     logit_scale: float = 1.0
+    embed_scale: float = 1.0
+    norm_groups: int = 1
+    tie_head: bool = False
 
 
 def _need(d: dict, key: str, where: str):
