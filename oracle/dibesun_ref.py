@@ -38,7 +38,8 @@ def chunk_sigmoid_attention(h, w, pre, m, eps):
     """Keys of the query's own chunk (chunks counted from position 0) up to the query; weight sigmoid(capped score + b_h)."""
     T = h.shape[0]
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    C, scale, cap = int(m["mask"]["size"]), float(m["scale"]), float(m["softcap"])
+    C = int(m["mask"]["size"]) if m.get("mask") else T            # no mask entry: all earlier keys
+    scale, cap = float(m["scale"]), float(m.get("softcap", 0.0))   # no cap entry (or 0): scores as they are
     q = (unit_rms(h @ w[pre + "q"].T, eps) * w[pre + "q.norm"]).reshape(T, H, d)
     k = (unit_rms(h @ w[pre + "k"].T, eps) * w[pre + "k.norm"]).reshape(T, G, d)
     v = (h @ w[pre + "v"].T).reshape(T, G, dv)
@@ -48,7 +49,8 @@ def chunk_sigmoid_attention(h, w, pre, m, eps):
         for hh in range(H):
             g = hh // (H // G)
             s = (k[j0:i + 1, g] @ q[i, hh]) * scale
-            s = cap * np.tanh(s / cap)
+            if cap > 0.0:
+                s = cap * np.tanh(s / cap)
             out[i, hh] = sigmoid(s + w[pre + "pb"][hh]) @ v[j0:i + 1, g]
     return out.reshape(T, H * dv) @ w[pre + "o"].T
 
