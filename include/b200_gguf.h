@@ -148,13 +148,31 @@ int b2_synchronize(b2_engine* e);
 #define B2_MIX_CHUNK_LINEAR 6    /* chunk-local attention with sigmoid key weights (whole-projection query / key norm, capped
                                     scores, per-head bias, no rotation) beside a linear attention with one fixed decay per head
                                     (SiLU feature maps, gated RMS norm over all heads); the outputs are added with fixed weights */
+#define B2_MIX_SINK_DELTA 7      /* softmax attention (sliding window, a learned sink term in each head's denominator, partial
+                                    rotate-half rotation, the heads' weights mixed across heads, one sigmoid gate per head) beside a
+                                    gated delta rule with ONE input-dependent decay per head; the two outputs are RMS-normed over the
+                                    width and averaged */
+#define B2_MIX_SINK_ATTN 8       /* the same softmax attention alone; what differs is chosen by attn_flags */
 #define B2_FF_RELU2 0            /* squared-ReLU block with biases (when n_ff > 0) */
 #define B2_FF_MOE 1              /* routed mixture of gated (SiLU) experts, n_ff = width of one expert */
 #define B2_FF_GLU 2              /* gated SiLU unit without biases: down(silu(gate x) * (up x)) */
+#define B2_FF_PIECEWISE 3        /* down(act(up x)) without biases; act(z) = a z^2 + z / 2 for z > 0, b (exp(z) - 1 - z) + z / 2 otherwise,
+                                    a = softplus(p), b = 1/2 + softplus(q) with (p, q) in tensor mlp.act */
+#define B2_EXPERT_SILU 0         /* expert: down(silu(gate x) * (up x)) */
+#define B2_EXPERT_CLAMPED 1      /* expert: g = min(gate x, limit), u = clamp(up x, -limit, limit); down(g * sigmoid(alpha g) * (u + 1)) */
+#define B2_ATTN_BIAS 1           /* attn_flags: q, k, v projections carry biases (tensors q.b, k.b, v.b) */
+#define B2_ATTN_UNIT_QK 2        /* after the rotation every head's q and k are divided by their RMS (no weight) */
+#define B2_ATTN_TALK 4           /* weight_h(i, j) <- sum_g talk[h][g] weight_g(i, j) after the softmax (tensor talk [H][H]) */
+#define B2_ATTN_HEAD_GATE 8      /* the sigmoid output gate is one number per head (tensor g [H][W]); else one per output entry */
 #define B2_ROUTE_SOFTMAX_ALL 0   /* scores = softmax over all slots; an additive correction steers the choice only */
 #define B2_ROUTE_TOPK_SOFTMAX 1  /* biased logits choose; weights = softmax over the chosen logits */
 #define B2_BLOCK_POSTSUM_LN 0    /* x <- LayerNorm(alpha * x + f(x)) */
 #define B2_BLOCK_PRENORM_RMS 1   /* x <- x + m * f(RMSNorm(x) * (1 + w)); the embedding and the output are normed the same way */
+#define B2_BLOCK_HYPER_RMS 3     /* n_streams copies x_1..x_S of the stream (all the embedding at first). A sublayer reads
+                                    h = RMSNorm(sum_s in[s] x_s) * w, passed through a causal convolution with a skip when canon_taps > 0
+                                    (h + conv(h), tensors l<i>.canon1/2 [W][taps]); its output y goes back as
+                                    x_t <- sum_s mix[s][t] x_s + out[t] y (tensors l<i>.hc1/2.in, .mix, .out; absent: plain residual).
+                                    The output norm reads the sum of the copies. */
 #define B2_BLOCK_OUTNORM_RMS 2   /* x <- x + RMSNorm_parts(f(x)) * w: the branch OUTPUT is normed, over norm_groups equal parts;
                                     the output norm has the same form */
 typedef struct b2_layer_desc {
@@ -184,6 +202,15 @@ typedef struct b2_layer_desc {
     int32_t attn_vdim, pad2_;
     double softcap;           /* score <- softcap * tanh(score / softcap); <= 0: scores are not capped */
     double branch_scale[2];   /* weights of the two branches in the sum */
+    /* softmax attention with a sink (n_head, n_head_kv, head_dim, attn_vdim, rot_dims, rope_base, window (<= 0: none), attn_scale as
+     * above) and the head-decay delta rule (mm_heads, key_heads, mm_dim, mm_vdim, conv_taps) */
+    int32_t attn_flags;       /* B2_ATTN_* */
+    int32_t weights_of;       /* 1 + index of the layer whose tensors this entry uses (a repeated run of layers shares weights; every
+                                 entry keeps cache and state of its own); 0: its own */
+    int32_t moe_expert;       /* B2_EXPERT_* */
+    int32_t moe_renorm;       /* != 0: the chosen scores are divided by their sum (+ 1e-20) */
+    double moe_limit;         /* B2_EXPERT_CLAMPED */
+    double moe_alpha;         /* B2_EXPERT_CLAMPED: slope inside the sigmoid */
 } b2_layer_desc;
 typedef struct b2_layered_config {
     int32_t n_layer, n_embd, n_vocab;
@@ -198,6 +225,8 @@ typedef struct b2_layered_config {
     float embed_scale;        /* the embedding row times this (0 is read as 1) */
     int32_t norm_groups;      /* B2_BLOCK_OUTNORM_RMS: equal consecutive parts of the width, each normed by itself (0 is read as 1) */
     int32_t tie_head;         /* != 0: the output map is the embedding table (no tensor "head") */
+    int32_t n_streams;        /* B2_BLOCK_HYPER_RMS: copies of the residual stream (0 is read as 1) */
+    int32_t canon_taps;       /* B2_BLOCK_HYPER_RMS: taps of the convolution on every sublayer's input (0: none) */
 } b2_layered_config;
 /* Then b2_upload_tensor for every tensor (BF16 / F32), b2_engine_finalize, b2_seq_set_blocks / b2_seq_begin (n_past must be
  * 0: recurrent state cannot be rewound; it zeroes the slot's state) as for any engine. */

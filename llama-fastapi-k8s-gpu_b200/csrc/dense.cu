@@ -25,7 +25,7 @@ struct DenseDev {
     const float* bias;
     float* y; int ldy;
     int T, N, K, epi;
-    float scale;
+    float scale, p0, p1;
     const float* aux; int ldaux;
     long x_bs, w_bs, y_bs, aux_bs;
     int grouped;                   // 0 plain, 1 one pair per blockIdx.y, 2 tiles
@@ -65,12 +65,18 @@ __device__ __forceinline__ void epi_store(const DenseDev& a, float* y, const flo
     if (a.epi == EPI_BIAS || a.epi == EPI_BIAS_RELU2) { if (a.bias) v += a.bias[n]; }
     if (a.epi == EPI_BIAS_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
     if (a.epi == EPI_MUL_SIGMOID) v *= 1.f / (1.f + expf(-aux[(size_t)t * a.ldaux + n]));
+    if (a.epi == EPI_PIECEWISE) v = v > 0.f ? fmaf(a.p0 * v, v, 0.5f * v) : fmaf(a.p1, expm1f(v) - v, 0.5f * v);
     y[(size_t)t * a.ldy + n] = v * a.scale;
 }
 // two neighbouring columns n (even) and n + 1
 __device__ __forceinline__ void epi_store2(const DenseDev& a, float* y, const float* aux, int t, int n, float v0, float v1) {
     if (a.epi == EPI_GLU_SILU) {
         if (n + 1 < a.N) y[(size_t)t * a.ldy + (n >> 1)] = silu_act(v0) * v1 * a.scale;
+        return;
+    }
+    if (a.epi == EPI_GLU_CLAMP) {
+        const float g = fminf(v0, a.p0), u = fminf(fmaxf(v1, -a.p0), a.p0);
+        if (n + 1 < a.N) y[(size_t)t * a.ldy + (n >> 1)] = g / (1.f + expf(-a.p1 * g)) * (u + 1.f) * a.scale;
         return;
     }
     if (n < a.N) epi_store(a, y, aux, t, n, v0);
@@ -182,7 +188,7 @@ static cudaError_t launch_rows(const DenseDev& d, int batch, cudaStream_t s) {
     const unsigned gy = d.grouped ? d.T : 1, gz = d.grouped ? 1 : batch;       // grouped: one pair row per blockIdx.y
     const int N = d.N;
     if (d.grouped || d.T == 1) {
-        if (d.epi == EPI_GLU_SILU) return launch_chain(dense_rows_kernel<TW, 1, 2>, dim3((N + 15) / 16, gy, gz), block, 0, s, d);
+        if (d.epi == EPI_GLU_SILU || d.epi == EPI_GLU_CLAMP) return launch_chain(dense_rows_kernel<TW, 1, 2>, dim3((N + 15) / 16, gy, gz), block, 0, s, d);
         return launch_chain(dense_rows_kernel<TW, 1, 1>, dim3((N + 7) / 8, gy, gz), block, 0, s, d);
     }
     if (d.T == 2) return launch_chain(dense_rows_kernel<TW, 2, 2>, dim3((N + 15) / 16, gy, gz), block, 0, s, d);
@@ -425,12 +431,12 @@ __global__ void __launch_bounds__(256, 2) dense_mma_big_kernel(const __nv_bfloat
 cudaError_t dense_launch(const DenseArgs& a, cudaStream_t s) {
     if (a.T <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return cudaErrorInvalidValue;
     if (a.w_type != T_BF16 && a.w_type != T_F32) return cudaErrorInvalidValue;
-    if (a.epi == EPI_GLU_SILU && a.N % 2) return cudaErrorInvalidValue;
+    if ((a.epi == EPI_GLU_SILU || a.epi == EPI_GLU_CLAMP) && a.N % 2) return cudaErrorInvalidValue;
     if (a.groups && a.batch != 1) return cudaErrorInvalidValue;
     const bool wb = a.w_type == T_BF16;
     DenseDev d = {};
     d.x = a.x; d.ldx = a.ldx; d.w = a.w; d.bias = a.bias; d.y = a.y; d.ldy = a.ldy; d.T = a.T; d.N = a.N; d.K = a.K; d.epi = a.epi;
-    d.scale = a.scale; d.aux = a.aux; d.ldaux = a.ldaux; d.x_bs = a.x_bs; d.w_bs = a.w_bs; d.y_bs = a.y_bs; d.aux_bs = a.aux_bs;
+    d.scale = a.scale; d.p0 = a.p0; d.p1 = a.p1; d.aux = a.aux; d.ldaux = a.ldaux; d.x_bs = a.x_bs; d.w_bs = a.w_bs; d.y_bs = a.y_bs; d.aux_bs = a.aux_bs;
     if (a.groups) { d.g = *a.groups; d.grouped = a.groups->tile_group ? 2 : 1; }
     if (d.grouped == 1 || (!d.grouped && a.T <= ROWS_MAX_T)) return wb ? launch_rows<__nv_bfloat16>(d, a.batch, s) : launch_rows<float>(d, a.batch, s);
     // few output columns in 32-bit (router scores): the tiled kernel would run a handful of CTAs over the whole K; the

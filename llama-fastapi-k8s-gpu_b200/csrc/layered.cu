@@ -59,6 +59,15 @@ struct LyLayer {
     DenseW cl_proj, cl_o;
     int rq_off = 0;
     float *pb = nullptr, *decay = nullptr, *la_state = nullptr;
+    // softmax attention with a sink (alone, or beside the head-decay delta rule): sk_proj rows left q | k | v | g (| right q | k | v
+    // | b | a | g); reuses attn_o, sink, left_w, right_w, rot_*, k_pool, v_pool and the delta rule's st_* fields
+    DenseW sk_proj;
+    int gl_off = 0, ra_off = 0, rg_off = 0;
+    float *sk_bias = nullptr, *talk = nullptr;
+    // several copies of the stream: per sublayer (0 mixer, 1 feed-forward) read weights, mixing matrix, write weights; the
+    // convolution on the sublayer's input and the last taps-1 inputs per slot
+    float *hc_in[2] = {}, *hc_mix[2] = {}, *hc_out[2] = {}, *canon_w[2] = {}, *canon_state[2] = {};
+    float act_p0 = 0.f, act_p1 = 0.f;          // piecewise activation: softplus(p), 1/2 + softplus(q)
 };
 
 struct StepGraph { cudaGraphExec_t exec = nullptr; int n_launch = 0; bool failed = false; };
@@ -72,6 +81,7 @@ struct LayeredModel {
     bool exact = false;                // B2_FLAG_F32
     int** block_tables = nullptr;      // device [max_seqs] -> page table
     // step workspace (max_step_tokens rows)
+    float *xs = nullptr, *hc = nullptr, *cross = nullptr;     // copies of the stream [S][max_step_tokens][W]; convolved sublayer input; per-(query head, value head) attention sums
     float *x = nullptr, *proj = nullptr, *buf[4] = {}, *oL = nullptr, *oR = nullptr, *hn = nullptr, *ff = nullptr, *rows = nullptr, *logits = nullptr;
     __nv_bfloat16* xb = nullptr;       // a product's input rounded to bf16 [max_step_tokens][widest input]
     std::unordered_map<std::string, StepGraph> graphs;     // replayable small steps, by shape (b2_step)
@@ -264,12 +274,104 @@ int layered_finalize(b2_engine* e) {
     const size_t cache_esz = m->exact ? 4 : 2;
     size_t max_proj = 1, max_buf = 1, max_ff = 1, max_attn = 0, max_attn_d = 0, max_glu = 0;
     size_t moe_pairs = 0, moe_slots = 0, moe_ff = 0, moe_experts = 0, moe_xb = 0;     // moe_xb: expert activations per step token
+    const bool hyper = c.block_style == B2_BLOCK_HYPER_RMS;
+    const int n_streams = std::max(1, c.n_streams);
+    size_t max_cross = 0;
+    // cache pages and recurrent state of a sink-attention layer (every run of a repeated layer has its own)
+    auto sink_state = [&](LyLayer& L) -> int {
+        const b2_layer_desc& d = L.d;
+        int rc2;
+        const size_t kpool = (size_t)c.kv_num_blocks * d.n_head_kv * c.kv_block_tokens * d.head_dim * cache_esz;
+        const size_t vpool = (size_t)c.kv_num_blocks * d.n_head_kv * c.kv_block_tokens * d.attn_vdim * cache_esz;
+        if ((rc2 = dev_alloc(m, &L.k_pool, kpool, true))) return rc2;
+        if ((rc2 = dev_alloc(m, &L.v_pool, vpool, true))) return rc2;
+        e->kv_bytes += (int64_t)(kpool + vpool);
+        if (d.mixer == B2_MIX_SINK_DELTA) {
+            if ((rc2 = dev_alloc(m, (void**)&L.st_conv_state, (size_t)S * std::max(1, d.conv_taps - 1) * L.conv_C * 4, true))) return rc2;
+            if ((rc2 = dev_alloc(m, (void**)&L.st_state, (size_t)S * col_state_floats(d.mm_heads, d.mm_dim, d.mm_vdim) * 4, true))) return rc2;
+        }
+        return B2_OK;
+    };
+    auto canon_state = [&](LyLayer& L) -> int {
+        for (int q = 0; q < 2; q++) {
+            L.canon_state[q] = nullptr;
+            if (!L.canon_w[q]) continue;
+            const int rc2 = dev_alloc(m, (void**)&L.canon_state[q], (size_t)S * std::max(1, c.canon_taps - 1) * W * 4, true);
+            if (rc2) return rc2;
+        }
+        return B2_OK;
+    };
     for (int li = 0; li < c.n_layer; li++) {
         LyLayer& L = m->layers[li];
         const b2_layer_desc& d = L.d;
-        const std::string p = "l" + std::to_string(li) + ".";
+        const int wl = d.weights_of > 0 ? d.weights_of - 1 : li;
+        const std::string p = "l" + std::to_string(wl) + ".";
+        const bool sink_kind = d.mixer == B2_MIX_SINK_DELTA || d.mixer == B2_MIX_SINK_ATTN;
+        if (sink_kind) {
+            // a repeated run shares the weights of the first run of the same layer and gets a cache and state of its own
+            int earlier = -1;
+            for (int j = 0; j < li && earlier < 0; j++) if (m->layers[j].d.weights_of > 0 && m->layers[j].d.weights_of == d.weights_of) earlier = j;
+            if (earlier >= 0) {
+                const b2_layer_desc mine = L.d;
+                L = m->layers[earlier];
+                L.d = mine;
+                if ((rc = sink_state(L)) || (rc = canon_state(L))) return rc;
+                continue;
+            }
+        }
         if ((rc = vec_f32(e, m, p + "norm1", W, 1, &L.norm1))) return rc;
-        if (d.mixer == B2_MIX_WINDOW_SCAN) {
+        if (hyper) {
+            for (int q = 0; q < (d.n_ff > 0 ? 2 : 1); q++) {
+                const std::string hc = p + "hc" + std::to_string(q + 1) + ".";
+                if (e->tensors.count(hc + "mix")) {
+                    if ((rc = vec_f32(e, m, hc + "in", n_streams, 1, &L.hc_in[q]))) return rc;
+                    if ((rc = vec_f32(e, m, hc + "mix", n_streams, n_streams, &L.hc_mix[q]))) return rc;
+                    if ((rc = vec_f32(e, m, hc + "out", n_streams, 1, &L.hc_out[q]))) return rc;
+                } else if (n_streams > 1) return b2_fail(B2_ERR_STATE, "missing tensor " + hc + "mix");
+                if (c.canon_taps > 0 && (rc = vec_f32(e, m, p + "canon" + std::to_string(q + 1), c.canon_taps, W, &L.canon_w[q]))) return rc;
+            }
+            if ((rc = canon_state(L))) return rc;
+        }
+        if (sink_kind) {
+            const bool two = d.mixer == B2_MIX_SINK_DELTA;
+            const std::string a = two ? p + "mix.left." : p + "mix.", b = p + "mix.right.";
+            const int H = d.n_head, G = d.n_head_kv, qd = H * d.head_dim, kd = G * d.head_dim, vd = G * d.attn_vdim, od = H * d.attn_vdim;
+            const int gd = (d.attn_flags & B2_ATTN_HEAD_GATE) ? H : od;
+            const int Hr = d.mm_heads, rkd = d.key_heads * d.mm_dim, rvd = Hr * d.mm_vdim;
+            std::vector<std::pair<std::string, int>> parts = {{a + "q", qd}, {a + "k", kd}, {a + "v", vd}, {a + "g", gd}};
+            if (two) for (auto& pr : std::vector<std::pair<std::string, int>>{{b + "q", rkd}, {b + "k", rkd}, {b + "v", rvd}, {b + "b", Hr}, {b + "a", Hr}, {b + "g", rvd}}) parts.push_back(pr);
+            std::vector<int> offs;
+            if ((rc = fuse(e, m, parts, W, L.sk_proj, offs))) return rc;
+            L.q_off = offs[0]; L.k_off = offs[1]; L.v_off = offs[2]; L.gl_off = offs[3];
+            if (d.attn_flags & B2_ATTN_BIAS) {       // one bias row for the fused product; the gate has none
+                if ((rc = dev_alloc(m, (void**)&L.sk_bias, (size_t)L.sk_proj.N * 4, true))) return rc;
+                const std::pair<std::string, int> bs[3] = {{a + "q.b", qd}, {a + "k.b", kd}, {a + "v.b", vd}};
+                for (int k = 0; k < 3; k++) {
+                    DevTensor t;
+                    if ((rc = find(e, bs[k].first, bs[k].second, 1, t))) return rc;
+                    to_f32_kernel<<<(unsigned)((bs[k].second + 255) / 256), 256, 0, e->stream>>>(t.type, t.ptr, bs[k].second, L.sk_bias + offs[k]);
+                    CK(cudaGetLastError());
+                }
+            }
+            if (e->tensors.count(a + "sink") && (rc = vec_f32(e, m, a + "sink", H, 1, &L.sink))) return rc;
+            if ((d.attn_flags & B2_ATTN_TALK) && (rc = vec_f32(e, m, a + "talk", H, H, &L.talk))) return rc;
+            if ((rc = matrix(e, a + "o", W, od, L.attn_o))) return rc;
+            if ((rc = build_rotary(e, m, L))) return rc;
+            if (two) {
+                L.conv_off = offs[4]; L.conv_C = 2 * rkd + rvd; L.b_off = offs[7]; L.ra_off = offs[8]; L.rg_off = offs[9];
+                if ((rc = concat_f32(e, m, {{b + "q.conv", rkd}, {b + "k.conv", rkd}, {b + "v.conv", rvd}}, d.conv_taps, &L.st_conv_w))) return rc;
+                if ((rc = vec_f32(e, m, b + "A_log", Hr, 1, &L.st_A_log))) return rc;
+                if ((rc = vec_f32(e, m, b + "dt_bias", Hr, 1, &L.st_dt_bias))) return rc;
+                if ((rc = vec_f32(e, m, b + "norm", d.mm_vdim, 1, &L.st_norm))) return rc;
+                if ((rc = matrix(e, b + "o", W, rvd, L.st_o))) return rc;
+                if ((rc = vec_f32(e, m, a + "out", W, 1, &L.left_w))) return rc;
+                if ((rc = vec_f32(e, m, b + "out", W, 1, &L.right_w))) return rc;
+            }
+            if ((rc = sink_state(L))) return rc;
+            max_proj = std::max<size_t>(max_proj, L.sk_proj.N);
+            max_buf = std::max<size_t>({max_buf, (size_t)qd, (size_t)od, two ? (size_t)L.conv_C : 1, two ? (size_t)rvd : 1});
+            if (d.attn_flags & B2_ATTN_TALK) max_cross = std::max<size_t>(max_cross, (size_t)H * G * d.attn_vdim);
+        } else if (d.mixer == B2_MIX_WINDOW_SCAN) {
             const std::string a = p + "mix.left.", b = p + "mix.right.";
             const int qd = d.n_head * d.head_dim, kd = d.n_head_kv * d.head_dim;
             std::vector<int> offs;
@@ -422,7 +524,8 @@ int layered_finalize(b2_engine* e) {
             const int slots = d.moe_experts + d.moe_identity;
             if ((rc = vec_f32(e, m, p + "norm2", W, 1, &L.norm2))) return rc;
             if ((rc = matrix(e, p + "mlp.router", slots, W, L.router))) return rc;
-            if ((rc = vec_f32(e, m, p + (d.moe_route == B2_ROUTE_TOPK_SOFTMAX ? "mlp.router.b" : "mlp.correction"), slots, 1, &L.correction))) return rc;
+            const std::string cn = p + (d.moe_route == B2_ROUTE_TOPK_SOFTMAX ? "mlp.router.b" : "mlp.correction");
+            if ((!hyper || e->tensors.count(cn)) && (rc = vec_f32(e, m, cn, slots, 1, &L.correction))) return rc;
             if ((rc = stack_experts(e, m, p + "mlp.e", d.moe_experts, d.n_ff, W, L.gate_up, L.e_down))) return rc;
             if (d.moe_shared_ff > 0) {
                 if ((rc = stack_experts(e, m, p + "mlp.shared", 0, d.moe_shared_ff, W, L.glu_gate_up, L.glu_down))) return rc;
@@ -433,6 +536,18 @@ int layered_finalize(b2_engine* e) {
             moe_ff = std::max<size_t>(moe_ff, d.n_ff);
             moe_xb = std::max<size_t>(moe_xb, (size_t)d.moe_top * d.n_ff);
             moe_experts = std::max<size_t>(moe_experts, d.moe_experts);
+        } else if (d.n_ff > 0 && d.ff_kind == B2_FF_PIECEWISE) {
+            float* act = nullptr;
+            float host[2] = {0.f, 0.f};
+            if ((rc = vec_f32(e, m, p + "norm2", W, 1, &L.norm2))) return rc;
+            if ((rc = matrix(e, p + "mlp.up", d.n_ff, W, L.up))) return rc;
+            if ((rc = matrix(e, p + "mlp.down", W, d.n_ff, L.down))) return rc;
+            if ((rc = vec_f32(e, m, p + "mlp.act", 2, 1, &act))) return rc;
+            CK(cudaStreamSynchronize(e->stream));
+            CK(cudaMemcpy(host, act, 8, cudaMemcpyDeviceToHost));
+            auto softplus = [](double z) { return z > 0.0 ? z + log1p(exp(-z)) : log1p(exp(z)); };
+            L.act_p0 = (float)softplus(host[0]); L.act_p1 = (float)(0.5 + softplus(host[1]));
+            max_ff = std::max<size_t>(max_ff, d.n_ff);
         } else if (d.n_ff > 0 && d.ff_kind == B2_FF_GLU) {
             if ((rc = vec_f32(e, m, p + "norm2", W, 1, &L.norm2))) return rc;
             if ((rc = stack_experts(e, m, p + "mlp", 0, d.n_ff, W, L.glu_gate_up, L.glu_down))) return rc;
@@ -447,6 +562,11 @@ int layered_finalize(b2_engine* e) {
         }
     }
     if ((rc = dev_alloc(m, (void**)&m->x, (size_t)Tm * W * 4))) return rc;
+    if (hyper) {
+        if ((rc = dev_alloc(m, (void**)&m->xs, (size_t)n_streams * Tm * W * 4))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->hc, (size_t)Tm * W * 4))) return rc;
+        if (max_cross > 0 && (rc = dev_alloc(m, (void**)&m->cross, (size_t)Tm * max_cross * 4))) return rc;
+    }
     if ((rc = dev_alloc(m, (void**)&m->proj, (size_t)Tm * max_proj * 4))) return rc;
     for (int i = 0; i < 4; i++) if ((rc = dev_alloc(m, (void**)&m->buf[i], (size_t)Tm * max_buf * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->oL, (size_t)Tm * W * 4))) return rc;
@@ -505,7 +625,18 @@ int layered_seq_reset(b2_engine* e, int slot) {
     LayeredModel* m = e->layered;
     for (auto& L : m->layers) {
         const b2_layer_desc& d = L.d;
-        if (d.mixer == B2_MIX_WINDOW_SCAN) {
+        for (int q = 0; q < 2; q++)
+            if (L.canon_state[q]) {
+                const size_t cs = (size_t)std::max(1, m->c.canon_taps - 1) * m->c.n_embd;
+                CK(cudaMemsetAsync(L.canon_state[q] + slot * cs, 0, cs * 4, e->stream));
+            }
+        if (d.mixer == B2_MIX_SINK_ATTN) {
+            // nothing but cache pages, which are overwritten
+        } else if (d.mixer == B2_MIX_SINK_DELTA) {
+            const size_t cs = (size_t)std::max(1, d.conv_taps - 1) * L.conv_C, ss = col_state_floats(d.mm_heads, d.mm_dim, d.mm_vdim);
+            CK(cudaMemsetAsync(L.st_conv_state + slot * cs, 0, cs * 4, e->stream));
+            CK(cudaMemsetAsync(L.st_state + slot * ss, 0, ss * 4, e->stream));
+        } else if (d.mixer == B2_MIX_WINDOW_SCAN) {
             const size_t cs = (size_t)d.d_inner * std::max(1, d.conv_taps - 1), ss = (size_t)d.d_inner * d.d_state;
             CK(cudaMemsetAsync(L.conv_state + slot * cs, 0, cs * 4, e->stream));
             CK(cudaMemsetAsync(L.ssm_state + slot * ss, 0, ss * 4, e->stream));
@@ -571,7 +702,18 @@ extern "C" int b2_engine_create_layered(const b2_layered_config* c, const b2_lay
             if (d.head_dim > 256 || d.attn_vdim > 256) return b2_fail(B2_ERR_UNSUPPORTED, li + "key or value size above 256");
             if (d.mm_heads <= 0 || d.mm_dim <= 0 || d.mm_vdim <= 0) return b2_fail(B2_ERR_ARG, li + "bad linear-attention sizes");
             if (d.mm_dim > 256) return b2_fail(B2_ERR_UNSUPPORTED, li + "linear-attention key size above 256");
+        } else if (d.mixer == B2_MIX_SINK_DELTA || d.mixer == B2_MIX_SINK_ATTN) {
+            if (d.n_head <= 0 || d.n_head_kv <= 0 || d.n_head % d.n_head_kv || d.head_dim <= 0 || d.attn_vdim <= 0) return b2_fail(B2_ERR_ARG, li + "bad head counts");
+            if (d.head_dim > 256 || d.attn_vdim > 256) return b2_fail(B2_ERR_UNSUPPORTED, li + "key or value size above 256");
+            if (d.rot_dims < 0 || d.rot_dims > d.head_dim || d.rot_dims % 2) return b2_fail(B2_ERR_ARG, li + "rotary dims must be even and <= the head size");
+            if (d.mixer == B2_MIX_SINK_DELTA) {
+                if (d.mm_heads <= 0 || d.key_heads <= 0 || d.mm_heads % d.key_heads || d.mm_dim <= 0 || d.mm_vdim <= 0 || d.conv_taps <= 0 || d.conv_taps > 64)
+                    return b2_fail(B2_ERR_ARG, li + "bad delta-rule sizes");
+                if (d.mm_dim > 256) return b2_fail(B2_ERR_UNSUPPORTED, li + "delta-rule key size above 256");
+            }
+            if (c->block_style != B2_BLOCK_HYPER_RMS) return b2_fail(B2_ERR_UNSUPPORTED, li + "this mixer belongs to blocks with stream copies");
         } else return b2_fail(B2_ERR_UNSUPPORTED, li + "unknown mixer kind");
+        if (d.weights_of < 0 || d.weights_of > c->n_layer) return b2_fail(B2_ERR_ARG, li + "weights_of out of range");
         if (d.n_ff > 0 && d.ff_kind == B2_FF_MOE) {
             const int slots = d.moe_experts + d.moe_identity;
             if (d.moe_experts <= 0 || d.moe_identity < 0 || d.moe_top <= 0 || d.moe_top > slots || d.moe_groups <= 0 || slots % d.moe_groups ||
@@ -581,12 +723,22 @@ extern "C" int b2_engine_create_layered(const b2_layered_config* c, const b2_lay
             if (d.moe_route != B2_ROUTE_SOFTMAX_ALL && d.moe_route != B2_ROUTE_TOPK_SOFTMAX) return b2_fail(B2_ERR_ARG, li + "unknown routing rule");
             if (d.moe_route == B2_ROUTE_TOPK_SOFTMAX && (d.moe_identity > 0 || d.moe_groups > 1)) return b2_fail(B2_ERR_UNSUPPORTED, li + "top-k softmax routing has no identity slots or groups");
             if (d.moe_shared_ff < 0) return b2_fail(B2_ERR_ARG, li + "negative shared-expert width");
-        } else if (d.ff_kind != B2_FF_RELU2 && d.ff_kind != B2_FF_GLU) return b2_fail(B2_ERR_UNSUPPORTED, li + "unknown feed-forward kind");
+            if (d.moe_expert != B2_EXPERT_SILU && d.moe_expert != B2_EXPERT_CLAMPED) return b2_fail(B2_ERR_ARG, li + "unknown expert kind");
+            if (d.moe_expert == B2_EXPERT_CLAMPED && !(d.moe_limit > 0.0)) return b2_fail(B2_ERR_ARG, li + "a clamped expert needs a positive limit");
+        } else if (d.ff_kind != B2_FF_RELU2 && d.ff_kind != B2_FF_GLU && d.ff_kind != B2_FF_PIECEWISE) return b2_fail(B2_ERR_UNSUPPORTED, li + "unknown feed-forward kind");
         if (c->block_style == B2_BLOCK_PRENORM_RMS ? (d.mixer == B2_MIX_WINDOW_SCAN) : false)
             return b2_fail(B2_ERR_UNSUPPORTED, li + "the two-branch mixer belongs to post-sum blocks");
     }
-    if (c->block_style != B2_BLOCK_POSTSUM_LN && c->block_style != B2_BLOCK_PRENORM_RMS && c->block_style != B2_BLOCK_OUTNORM_RMS)
+    if (c->block_style != B2_BLOCK_POSTSUM_LN && c->block_style != B2_BLOCK_PRENORM_RMS && c->block_style != B2_BLOCK_OUTNORM_RMS &&
+        c->block_style != B2_BLOCK_HYPER_RMS)
         return b2_fail(B2_ERR_ARG, "unknown block style");
+    if (c->block_style == B2_BLOCK_HYPER_RMS) {
+        if (c->n_streams < 0 || c->n_streams > 8) return b2_fail(B2_ERR_UNSUPPORTED, "at most 8 copies of the stream");
+        if (c->canon_taps < 0 || c->canon_taps > 64) return b2_fail(B2_ERR_ARG, "bad number of taps");
+        for (int i = 0; i < c->n_layer; i++)
+            if (layers[i].mixer != B2_MIX_SINK_DELTA && layers[i].mixer != B2_MIX_SINK_ATTN)
+                return b2_fail(B2_ERR_UNSUPPORTED, "layer " + std::to_string(i) + ": blocks with stream copies take the sink-attention mixers");
+    }
     if (c->block_style == B2_BLOCK_OUTNORM_RMS && (c->norm_groups < 0 || (c->norm_groups > 0 && c->n_embd % c->norm_groups)))
         return b2_fail(B2_ERR_ARG, "the norm's parts must divide the width");
     b2_engine* e = new b2_engine();
@@ -877,7 +1029,72 @@ static int mix_chunk_linear(b2_engine* e, LayeredModel* m, LyLayer& L, const Rag
     return dense(e, m, L.cl_o, m->buf[1], Kt, m->oL, W, T);
 }
 
+// softmax attention with a sink, alone (output in m->oL) or beside the head-decay delta rule (attention in m->oL, delta rule in
+// m->oR; the caller norms and averages them)
+static int mix_sink(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const b2_layered_config& c = m->c;
+    const b2_layer_desc& d = L.d;
+    cudaStream_t st = e->stream;
+    const int T = r.T, W = c.n_embd, Np = L.sk_proj.N, H = d.n_head, od = H * d.attn_vdim;
+    int rc;
+    if ((rc = dense(e, m, L.sk_proj, in, W, m->proj, Np, T, L.sk_bias, L.sk_bias ? EPI_BIAS : EPI_NONE))) return rc;
+    SinkAttnArgs a = {};
+    a.proj = m->proj; a.ldp = Np; a.q_off = L.q_off; a.k_off = L.k_off; a.v_off = L.v_off;
+    a.rot.cos = L.rot_cos; a.rot.sin = L.rot_sin; a.rot.rot_dims = d.rot_dims; a.unit_qk = (d.attn_flags & B2_ATTN_UNIT_QK) ? 1 : 0;
+    a.k_pool = L.k_pool; a.v_pool = L.v_pool; a.cache_f32 = m->exact ? 1 : 0; a.block_tables = m->block_tables; a.block_tokens = c.kv_block_tokens;
+    a.H = H; a.G = d.n_head_kv; a.d = d.head_dim; a.dv = d.attn_vdim; a.window = d.window; a.scale = (float)d.attn_scale; a.eps = c.norm_eps;
+    a.sink = L.sink; a.talk = L.talk; a.gate = m->proj + L.gl_off; a.ld_gate = Np; a.gate_per_head = (d.attn_flags & B2_ATTN_HEAD_GATE) ? 1 : 0;
+    a.q_rot = m->buf[0]; a.cross = m->cross; a.out = m->buf[1]; a.ld_out = od;
+    {
+        StepProfiler sp(m, st, 2);
+        CK(sink_attn_store_launch(a, r, st));
+        CK(sink_attn_launch(a, r, st));
+        e->launches += L.talk ? 3 : 2;
+    }
+    if ((rc = dense(e, m, L.attn_o, m->buf[1], od, m->oL, W, T))) return rc;
+    if (d.mixer != B2_MIX_SINK_DELTA) return B2_OK;
+    const int Hr = d.mm_heads, G = d.key_heads, kd = G * d.mm_dim, vd = Hr * d.mm_vdim;
+    ConvArgs cv = {};
+    cv.in = m->proj + L.conv_off; cv.ld_in = Np; cv.C = L.conv_C; cv.taps = d.conv_taps; cv.w = L.st_conv_w; cv.bias = nullptr;
+    cv.state = L.st_conv_state; cv.out = m->buf[0]; cv.ld_out = L.conv_C;
+    {
+        StepProfiler sp(m, st, 3);
+        CK(causal_conv_launch(cv, r, st));
+        CK(causal_conv_advance_launch(cv, r, st));
+        e->launches += d.conv_taps > 1 ? 2 : 1;
+    }
+    DeltaPrepArgs pa = {};
+    pa.q = m->buf[0]; pa.k = m->buf[0] + kd; pa.ld_qk = L.conv_C; pa.G = G; pa.d = d.mm_dim;
+    pa.a = m->proj + L.ra_off; pa.ld_a = Np; pa.A_log = L.st_A_log; pa.dt_bias = L.st_dt_bias; pa.H = Hr; pa.a_cols = 1;
+    pa.beta = m->proj + L.b_off; pa.ld_b = Np; pa.unit_eps = 1e-6f;
+    ColStateArgs cs = {};
+    cs.wk = m->buf[0] + kd; cs.ld_wk = L.conv_C; cs.rk = m->buf[0]; cs.ld_rk = L.conv_C;
+    cs.head_decay = m->proj + L.ra_off; cs.ld_hd = Np; cs.val = m->buf[0] + 2 * kd; cs.ld_v = L.conv_C;
+    cs.val_scale = m->proj + L.b_off; cs.ld_vs = Np; cs.H = Hr; cs.G = G; cs.R = d.mm_dim; cs.P = d.mm_vdim; cs.delta = 1;
+    cs.state = L.st_state; cs.y = m->buf[2]; cs.ld_y = vd;
+    GroupNormArgs gn = {};
+    gn.x = m->buf[2]; gn.ld_x = vd; gn.gate = m->proj + L.rg_off; gn.ld_g = Np; gn.w = L.st_norm; gn.w_gstride = 0; gn.groups = Hr; gn.n = d.mm_vdim;
+    gn.eps = c.norm_eps; gn.gate_first = 0; gn.gate_silu = 1; gn.y = m->buf[2]; gn.ld_y = vd;
+    {
+        StepProfiler sp(m, st, 4);
+        CK(delta_prepare_launch(pa, T, st));
+        CK(col_state_launch(cs, r, st));
+        CK(group_norm_gate_launch(gn, T, st));
+        e->launches += 3;
+    }
+    return dense(e, m, L.st_o, m->buf[2], vd, m->oR, W, T);
+}
+
 // ---- feed-forward blocks: input `in` [T][W], output in m->oL
+static int ff_piecewise(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const int T = r.T, W = m->c.n_embd;
+    DenseArgs up = {};
+    up.p0 = L.act_p0; up.p1 = L.act_p1;
+    int rc;
+    if ((rc = dense(e, m, L.up, in, W, m->ff, L.d.n_ff, T, nullptr, EPI_PIECEWISE, 1, &up))) return rc;
+    return dense(e, m, L.down, m->ff, L.d.n_ff, m->oL, W, T);
+}
+
 static int ff_relu2(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
     const int T = r.T, W = m->c.n_embd;
     int rc;
@@ -904,7 +1121,7 @@ static int ff_moe(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r,
     MoeRouteArgs ra = {};
     ra.logits = m->moe_logits; ra.ld = slots; ra.correction = L.correction; ra.n_slots = slots; ra.n_experts = d.moe_experts;
     ra.top = d.moe_top; ra.n_groups = d.moe_groups; ra.keep_groups = d.moe_keep; ra.scale = (float)d.moe_scale;
-    ra.mode = d.moe_route == B2_ROUTE_TOPK_SOFTMAX ? 1 : 0;
+    ra.mode = d.moe_route == B2_ROUTE_TOPK_SOFTMAX ? 1 : 0; ra.renorm = d.moe_renorm;
     ra.sel = m->moe_sel; ra.weight = m->moe_weight; ra.pair_token = m->moe_tok;
     DenseGroups g = {};
     g.n_groups = d.moe_experts;
@@ -930,7 +1147,8 @@ static int ff_moe(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r,
     DenseArgs up = {};
     g.x_rows = tiled ? m->moe_rows : m->moe_tok; g.w_stride = (long)2 * ff * W; g.x_total_rows = T;
     up.groups = &g;
-    if ((rc = dense(e, m, L.gate_up, in, W, m->moe_h, ff, pairs, nullptr, EPI_GLU_SILU, 1, &up))) return rc;
+    up.p0 = (float)d.moe_limit; up.p1 = (float)d.moe_alpha;
+    if ((rc = dense(e, m, L.gate_up, in, W, m->moe_h, ff, pairs, nullptr, d.moe_expert == B2_EXPERT_CLAMPED ? EPI_GLU_CLAMP : EPI_GLU_SILU, 1, &up))) return rc;
     DenseGroups g2 = g;
     g2.x_rows = nullptr; g2.w_stride = (long)W * ff; g2.x_total_rows = pairs;
     DenseArgs dn = {};
@@ -955,11 +1173,13 @@ static int run_mixer(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev&
         case B2_MIX_DELTA_RULE: return mix_delta_rule(e, m, L, r, in);
         case B2_MIX_SSD: return mix_ssd(e, m, L, r, in);
         case B2_MIX_CHUNK_LINEAR: return mix_chunk_linear(e, m, L, r, in);
+        case B2_MIX_SINK_DELTA: case B2_MIX_SINK_ATTN: return mix_sink(e, m, L, r, in);
     }
     return b2_fail(B2_ERR_UNSUPPORTED, "unknown mixer kind");
 }
 static int run_ff(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in, MoeJoinArgs* defer = nullptr) {
     if (L.d.ff_kind == B2_FF_MOE) return ff_moe(e, m, L, r, in, defer);
+    if (L.d.ff_kind == B2_FF_PIECEWISE) return ff_piecewise(e, m, L, r, in);
     return L.d.ff_kind == B2_FF_GLU ? ff_glu(e, m, L, r, in) : ff_relu2(e, m, L, r, in);
 }
 
@@ -991,6 +1211,58 @@ static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
         pending_moe = MoeJoinArgs{};
         return B2_OK;
     };
+    if (c.block_style == B2_BLOCK_HYPER_RMS) {
+        // The embedding sits in copy 0. A sublayer's output waits (in m->oL / m->oR / the mixture's rows) until the next boundary:
+        // one kernel writes it back into all copies, reads the next sublayer's input and norms it.
+        HyperJoinArgs hj = {};
+        MoeJoinArgs hj_moe = {};
+        bool first = true;
+        auto boundary = [&](const float* in_w, const float* norm_w, float* hn, float* sum_out) -> int {
+            StepProfiler sp(m, st, 5);
+            hj.xs = m->xs; hj.stream_stride = (long)c.max_step_tokens * W; hj.S = std::max(1, c.n_streams); hj.eps = c.norm_eps;
+            hj.in = in_w; hj.norm_w = norm_w; hj.hn = hn; hj.sum_out = sum_out; hj.bcast = first ? 1 : 0;
+            hj.moe = hj_moe.sel ? &hj_moe : nullptr;
+            CK(hyper_join_launch(hj, W, T, st));
+            e->launches++;
+            hj = HyperJoinArgs{}; hj_moe = MoeJoinArgs{};
+            first = false;
+            return B2_OK;
+        };
+        // the convolution around a skip on a sublayer's normed input; returns what the sublayer reads
+        auto canon = [&](LyLayer& L, int q) -> const float* {
+            if (!L.canon_w[q]) return m->hn;
+            ConvArgs cv = {};
+            cv.in = m->hn; cv.ld_in = W; cv.C = W; cv.taps = c.canon_taps; cv.w = L.canon_w[q]; cv.state = L.canon_state[q];
+            cv.out = m->hc; cv.ld_out = W; cv.skip = 1;
+            StepProfiler sp(m, st, 5);
+            if (causal_conv_launch(cv, r, st) != cudaSuccess || causal_conv_advance_launch(cv, r, st) != cudaSuccess) return nullptr;
+            e->launches += c.canon_taps > 1 ? 2 : 1;
+            return m->hc;
+        };
+        CK(cudaMemcpyAsync(m->xs, m->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
+        for (int li = 0; li < c.n_layer; li++) {
+            LyLayer& L = m->layers[li];
+            const b2_layer_desc& d = L.d;
+            if ((rc = boundary(L.hc_in[0], L.norm1, m->hn, nullptr))) return rc;
+            const float* in = canon(L, 0);
+            if (!in) return b2_fail(B2_ERR_CUDA, "input convolution launch failed");
+            if ((rc = run_mixer(e, m, L, r, in))) return rc;
+            hj.a = m->oL; hj.mix = L.hc_mix[0]; hj.out = L.hc_out[0];
+            if (d.mixer == B2_MIX_SINK_DELTA) { hj.wa = L.left_w; hj.b = m->oR; hj.wb = L.right_w; }
+            if (d.n_ff > 0) {
+                if ((rc = boundary(L.hc_in[1], L.norm2, m->hn, nullptr))) return rc;
+                if (!(in = canon(L, 1))) return b2_fail(B2_ERR_CUDA, "input convolution launch failed");
+                const bool moe = d.ff_kind == B2_FF_MOE;
+                if ((rc = run_ff(e, m, L, r, in, moe ? &hj_moe : nullptr))) return rc;
+                hj.a = moe ? nullptr : m->oL; hj.mix = L.hc_mix[1]; hj.out = L.hc_out[1];
+            }
+            if (m->trace || li == c.n_layer - 1) {
+                if ((rc = boundary(nullptr, nullptr, nullptr, m->x))) return rc;
+                if (m->trace) CK(cudaMemcpyAsync(m->trace + ((size_t)li * c.max_step_tokens) * W, m->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
+            }
+        }
+        return B2_OK;
+    }
     for (int li = 0; li < c.n_layer; li++) {
         LyLayer& L = m->layers[li];
         const b2_layer_desc& d = L.d;
@@ -1120,6 +1392,7 @@ extern "C" int b2_step(b2_engine* e, int n_entries, const int32_t* slots, const 
             CK(gather_rows_launch(m->x, W, d_rows + r0, nr, m->rows, st));
             if (c.block_style == B2_BLOCK_OUTNORM_RMS) CK(outnorm_join_launch(nullptr, m->rows, nullptr, m->final_norm, std::max(1, c.norm_groups), c.norm_eps, W, nr, m->rows, st));
             else if (c.block_style == B2_BLOCK_PRENORM_RMS) CK(resid_rms_norm_launch(m->rows, nullptr, 0.f, m->final_norm, 1.f, 1.f, c.norm_eps, W, nr, m->rows, st));
+            else if (c.block_style == B2_BLOCK_HYPER_RMS) CK(resid_rms_norm_launch(m->rows, nullptr, 0.f, m->final_norm, 0.f, 1.f, c.norm_eps, W, nr, m->rows, st));
             else CK(layer_norm_launch(m->rows, m->final_norm, c.norm_eps, W, nr, m->rows, st));
             e->launches += 2;
         }

@@ -32,7 +32,9 @@ struct RaggedDev {             // device pointers, valid for one step
 // Each output element is one fixed-order sum over k: a row's result does not depend on what else is in the batch.
 // EPI_GLU_SILU: weight rows come in pairs (2i = gate, 2i + 1 = up); output column i = silu(gate) * up, N counts weight rows.
 // EPI_MUL_SIGMOID: the product times sigmoid(aux[t][n]).
-enum DenseEpi { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_RELU2 = 2, EPI_GLU_SILU = 3, EPI_MUL_SIGMOID = 4 };
+// EPI_GLU_CLAMP: pairs as above; g = min(gate, p0), u = clamp(up, -p0, p0); output = g * sigmoid(p1 * g) * (u + 1).
+// EPI_PIECEWISE: z > 0: p0 z^2 + z / 2; else p1 (exp(z) - 1 - z) + z / 2.
+enum DenseEpi { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_RELU2 = 2, EPI_GLU_SILU = 3, EPI_MUL_SIGMOID = 4, EPI_GLU_CLAMP = 5, EPI_PIECEWISE = 6 };
 // Grouped products (mixture of experts): the rows of a step's (token, choice) pairs, each against the matrix of its group.
 //   tiles == nullptr: row p of the product is pair p itself, blockIdx.y walks the pairs one by one (few-token steps);
 //   else: pairs sorted by group, tile i = rows [tile_row0[i], + tile_rows[i]) of group tile_group[i]; *n_tiles of them.
@@ -60,6 +62,7 @@ struct DenseArgs {
     bool exact;                     // true: 32-bit multiply-adds (no tensor cores, inputs not rounded)
     __nv_bfloat16* xb;              // scratch [T][K] for X rounded to bf16 (large tensor-core steps); null: not available
     float scale = 1.f;              // the product (after the epilogue) times this
+    float p0 = 0.f, p1 = 0.f;       // constants of EPI_GLU_CLAMP / EPI_PIECEWISE
     const float* aux = nullptr; int ldaux = 0;      // EPI_MUL_SIGMOID
     // batch > 1: `batch` independent products, operand b at x + b * x_bs, w + b * w_bs (elements), y + b * y_bs, aux + b * aux_bs
     int batch = 1; long x_bs = 0, w_bs = 0, y_bs = 0, aux_bs = 0;
@@ -146,6 +149,7 @@ struct ConvArgs {
     const float* w; const float* bias;      // [C][taps]; [C] or null
     float* state;
     float* out; int ld_out;
+    int skip = 0;                            // 1: out = in + conv(in) without bias or activation (a convolution around a skip path)
 };
 cudaError_t causal_conv_launch(const ConvArgs& a, const RaggedDev& r, cudaStream_t s);
 // the state moves on to the last taps-1 inputs of every segment (after causal_conv_launch has read the old one)
@@ -181,6 +185,7 @@ struct DeltaPrepArgs {
     float* a; int ld_a; const float* A_log; const float* dt_bias; int H;
     float* beta; int ld_b;
     float unit_eps;
+    int a_cols = 0;                          // decay columns per head: 0 = d (one per key channel), 1 = one decay per head
 };
 cudaError_t delta_prepare_launch(const DeltaPrepArgs& a, int T, cudaStream_t s);
 // Mamba-2 step sizes, in place: dt [T][H] <- softplus(dt + dt_bias[h]); decay [T][H] = exp(-exp(A_log[h]) * dt)
@@ -192,6 +197,7 @@ struct GroupNormArgs {
     const float* x; int ld_x; const float* gate; int ld_g; const float* w; int w_gstride;
     int groups, n; float eps; int gate_first;
     float out_scale = 1.f;
+    int gate_silu = 0;                       // gate_first = 0 only: times silu(gate) instead of sigmoid(gate)
     float* y; int ld_y;
 };
 cudaError_t group_norm_gate_launch(const GroupNormArgs& a, int T, cudaStream_t s);
@@ -227,6 +233,7 @@ struct MoeRouteArgs {
     float scale;
     int mode = 0;                          // 0: weight = softmax over all slots (times scale), `correction` added for the choice only;
                                            // 1: logits + correction choose, weight = softmax over the chosen biased logits
+    int renorm = 0;                        // mode 0: the chosen scores are divided by their sum (+ 1e-20) before the scale
     int* sel; float* weight;               // [T][top]
     int* pair_token;                       // [T][top]: t (the input row of each pair)
 };
@@ -278,6 +285,52 @@ struct SigmoidAttnArgs {
 // norm of q and k, keys and values into the pages (and the SiLU columns)
 cudaError_t sigmoid_attn_store_launch(const SigmoidAttnArgs& a, const RaggedDev& r, cudaStream_t s);
 cudaError_t sigmoid_attn_launch(const SigmoidAttnArgs& a, const RaggedDev& r, cudaStream_t s);
+
+// ---------------------------------------------------------------- softmax attention with a sink (sink_attn.cu)
+// Grouped-query softmax attention over the paged cache: sliding window (position i sees j with 0 <= i - j < window; window
+// <= 0: all earlier keys), rotate-half rotation of the first rot_dims entries of every head of q and k, optionally unit-RMS q
+// and k after the rotation, and one extra term exp(sink[h]) in every head's denominator (no key, no value). With `talk` the
+// normalised weights of the heads are mixed, weight_h <- sum_g talk[h][g] weight_g, before head h applies them to the values
+// of ITS key/value head: the kernels then compute A[g][c] = sum_j weight_g(j) v_c(j) for every (query head g, value head c)
+// and a small pass forms out_h = gate_h * sum_g talk[h][g] A[g][c(h)]. The value size may differ from the key size.
+struct SinkAttnArgs {
+    const float* proj; int ldp; int q_off, k_off, v_off;      // projection rows: q [H*d], k [G*d], v [G*dv]
+    RotaryTable rot;                                           // pairs (i, i + rot_dims / 2)
+    int unit_qk;
+    void* k_pool; void* v_pool; int cache_f32;                 // pages [page][G][block_tokens][d] and [page][G][block_tokens][dv]
+    int* const* block_tables; int block_tokens;
+    int H, G, d, dv, window;
+    float scale, eps;
+    const float* sink;                                         // [H] or null
+    const float* talk;                                         // [H][H] or null
+    const float* gate; int ld_gate; int gate_per_head;         // sigmoid output gate read at gate[t * ld_gate + (h | h * dv + i)], or null
+    float* q_rot;                                              // scratch [T][H*d]
+    float* cross;                                              // scratch [T][H][G][dv] (talk only)
+    float* out; int ld_out;                                    // out[t][h*dv + i]
+};
+// rotation (and unit RMS) of q and k, keys and values into the pages
+cudaError_t sink_attn_store_launch(const SinkAttnArgs& a, const RaggedDev& r, cudaStream_t s);
+cudaError_t sink_attn_launch(const SinkAttnArgs& a, const RaggedDev& r, cudaStream_t s);
+
+// ---------------------------------------------------------------- several copies of the residual stream (hyper.cu)
+// The stream exists in S copies xs[s] (copy s of token t at xs + s * stream_stride + t * W). One pass per sublayer boundary:
+//   1. the pending sublayer output y[t] -- a dense row `a`, or (rms(a) wa + rms(b) wb) / 2 for a two-branch mixer, plus a
+//      mixture's weighted sum of expert rows -- is written back: x_t <- sum_s mix[s][t] x_s + out[t] y   (mix == null: x_t += y)
+//   2. the next sublayer's input is read: hn[t] = RMSNorm(sum_s in[s] x_s) * norm_w                        (in == null: x_0)
+//   3. sum_out[t] = sum_s x_s (for the output norm and for tracing)
+// Any of the three may be absent. bcast != 0: only copy 0 holds data yet; the others are read as equal to it and all are written
+// (the state right after the embedding).
+struct HyperJoinArgs {
+    float* xs; long stream_stride; int S;
+    const float* a; const float* wa; const float* b; const float* wb;      // pending output (a == null and no moe: nothing pending)
+    const MoeJoinArgs* moe;
+    const float* mix; const float* out;                                     // [S][S] indexed [from][to], [S]
+    const float* in; const float* norm_w; float* hn;                        // next read (hn == null: none)
+    float* sum_out;
+    int bcast;
+    float eps;
+};
+cudaError_t hyper_join_launch(const HyperJoinArgs& a, int W, int T, cudaStream_t s);
 
 // ---------------------------------------------------------------- graph (layered.cu)
 struct LayeredModel;

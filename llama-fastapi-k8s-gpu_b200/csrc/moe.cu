@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(32) moe_route_kernel(MoeRouteArgs a) {
     float sum = 0.f;
     for (int i = lane; i < n; i += 32) { const float e = expf(z[i] - mx); score[i] = e; sum += e; }
     sum = warp_sum(sum);
-    for (int i = lane; i < n; i += 32) { const float s = score[i] / sum; score[i] = s; choice[i] = s + a.correction[i]; }
+    for (int i = lane; i < n; i += 32) { const float s = score[i] / sum; score[i] = s; choice[i] = s + (a.correction ? a.correction[i] : 0.f); }
     __syncwarp();
     if (a.n_groups > 1 && a.keep_groups < a.n_groups) {
         const int per = n / a.n_groups;
@@ -72,6 +72,12 @@ __global__ void __launch_bounds__(32) moe_route_kernel(MoeRouteArgs a) {
             choice[idx] = NAN;                     // taken: NaN never wins a comparison
         }
         __syncwarp();
+    }
+    if (a.renorm) {                                // every lane the same sum, in pick order
+        float tot = 0.f;
+        for (int k = 0; k < a.top; k++) tot += a.weight[(size_t)t * a.top + k];
+        __syncwarp();
+        for (int k = lane; k < a.top; k += 32) a.weight[(size_t)t * a.top + k] /= tot / a.scale + 1e-20f;
     }
 }
 // grid (T), one warp: the `top` largest of logit + bias (ties to the lower index); weights = softmax over those alone.

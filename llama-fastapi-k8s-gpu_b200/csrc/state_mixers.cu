@@ -35,14 +35,14 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(ConvArgs a, RaggedDev 
     if (c >= a.C) return;
     const int seg = r.tok_seg[t], slot = r.seg_slot[seg], i = t - r.seg_start[seg];
     const int hist = a.taps - 1;
-    float acc = a.bias ? a.bias[c] : 0.f;
+    float acc = a.bias && !a.skip ? a.bias[c] : 0.f;
     for (int j = 0; j < a.taps; j++) {
         const int srci = i - hist + j;
         const float v = srci >= 0 ? a.in[(size_t)(t - i + srci) * a.ld_in + c]
                                   : a.state[((size_t)slot * hist + (hist + srci)) * a.C + c];
         acc = fmaf(a.w[(size_t)c * a.taps + j], v, acc);
     }
-    a.out[(size_t)t * a.ld_out + c] = silu_f(acc);
+    a.out[(size_t)t * a.ld_out + c] = a.skip ? a.in[(size_t)t * a.ld_in + c] + acc : silu_f(acc);
 }
 cudaError_t causal_conv_launch(const ConvArgs& a, const RaggedDev& r, cudaStream_t s) {
     return launch_chain(causal_conv_kernel, dim3(r.T, (a.C + 255) / 256), dim3(256), 0, s, a, r);
@@ -81,9 +81,10 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(DeltaPrepArgs a) {
         const float rinv = (is_q ? qmul : 1.f) / sqrtf(warp_sum(ss) + a.unit_eps);
         for (int i = lane; i < a.d; i += 32) v[i] *= rinv;
     }
-    for (int i = threadIdx.x; i < a.H * a.d; i += blockDim.x) {
+    const int ac = a.a_cols > 0 ? a.a_cols : a.d;
+    for (int i = threadIdx.x; i < a.H * ac; i += blockDim.x) {
         float* p = a.a + (size_t)t * a.ld_a + i;
-        *p = expf(-expf(a.A_log[i / a.d]) * softplus_f(*p + a.dt_bias[i]));
+        *p = expf(-expf(a.A_log[i / ac]) * softplus_f(*p + a.dt_bias[i]));
     }
     for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
         float* p = a.beta + (size_t)t * a.ld_b + h;
@@ -302,7 +303,7 @@ __global__ void __launch_bounds__(128) group_norm_gate_kernel(GroupNormArgs a) {
     const float* w = a.w + (size_t)g * a.w_gstride;
     float* y = a.y + (size_t)t * a.ld_y + (size_t)g * n;
     for (int i = threadIdx.x; i < n; i += blockDim.x)
-        y[i] = (a.gate_first ? x[i] * silu_f(gate[i]) * rinv * w[i] : x[i] * rinv * w[i] * sigmoid_f(gate[i])) * a.out_scale;
+        y[i] = (a.gate_first ? x[i] * silu_f(gate[i]) * rinv * w[i] : x[i] * rinv * w[i] * (a.gate_silu ? silu_f(gate[i]) : sigmoid_f(gate[i]))) * a.out_scale;
 }
 cudaError_t group_norm_gate_launch(const GroupNormArgs& a, int T, cudaStream_t s) {
     return launch_chain(group_norm_gate_kernel, dim3(T, a.groups), dim3(128), 0, s, a);

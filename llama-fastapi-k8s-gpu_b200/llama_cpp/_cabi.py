@@ -16,9 +16,12 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libb200gguf.so")
 B2_FLAG_NO_GRAPH, B2_FLAG_NO_PDL, B2_FLAG_ACT8, B2_FLAG_F32 = 1, 2, 4, 8
 B2_TYPE_F32, B2_TYPE_F16, B2_TYPE_I32, B2_TYPE_BF16 = 0, 1, 26, 30
 B2_MIX_WINDOW_SCAN, B2_MIX_MATRIX_MEMORY, B2_MIX_LATENT_ATTN, B2_MIX_DELTA_RULE, B2_MIX_SSD, B2_MIX_CHUNK_LINEAR = 1, 2, 3, 4, 5, 6
-B2_FF_RELU2, B2_FF_MOE, B2_FF_GLU = 0, 1, 2
+B2_MIX_SINK_DELTA, B2_MIX_SINK_ATTN = 7, 8
+B2_FF_RELU2, B2_FF_MOE, B2_FF_GLU, B2_FF_PIECEWISE = 0, 1, 2, 3
+B2_EXPERT_SILU, B2_EXPERT_CLAMPED = 0, 1
+B2_ATTN_BIAS, B2_ATTN_UNIT_QK, B2_ATTN_TALK, B2_ATTN_HEAD_GATE = 1, 2, 4, 8
 B2_ROUTE_SOFTMAX_ALL, B2_ROUTE_TOPK_SOFTMAX = 0, 1
-B2_BLOCK_POSTSUM_LN, B2_BLOCK_PRENORM_RMS, B2_BLOCK_OUTNORM_RMS = 0, 1, 2
+B2_BLOCK_POSTSUM_LN, B2_BLOCK_PRENORM_RMS, B2_BLOCK_OUTNORM_RMS, B2_BLOCK_HYPER_RMS = 0, 1, 2, 3
 B2_STEP_MAX_ENTRIES = 64
 
 
@@ -38,14 +41,15 @@ class B2LayerDesc(ctypes.Structure):
         (n, c_int32) for n in ("la_rot_dim", "la_vdim", "la_rank", "ff_kind", "key_heads", "rank_a", "rank_g", "norm_groups",
                                "moe_experts", "moe_identity", "moe_top", "moe_groups", "moe_keep", "pad1_")] + [
         ("moe_scale", c_double), ("moe_route", c_int32), ("moe_shared_ff", c_int32), ("attn_vdim", c_int32), ("pad2_", c_int32),
-        ("softcap", c_double), ("branch_scale", c_double * 2)]
+        ("softcap", c_double), ("branch_scale", c_double * 2)] + [
+        (n, c_int32) for n in ("attn_flags", "weights_of", "moe_expert", "moe_renorm")] + [("moe_limit", c_double), ("moe_alpha", c_double)]
 
 
 class B2LayeredConfig(ctypes.Structure):
     _fields_ = [(n, c_int32) for n in ("n_layer", "n_embd", "n_vocab")] + [("norm_eps", c_float), ("residual_scale", c_float)] + [
         (n, c_int32) for n in ("n_ctx", "max_seqs", "kv_block_tokens", "kv_num_blocks", "max_step_tokens", "device", "flags",
                                "block_style")] + [("logit_scale", c_float), ("embed_scale", c_float), ("norm_groups", c_int32),
-                                                  ("tie_head", c_int32)]
+                                                  ("tie_head", c_int32), ("n_streams", c_int32), ("canon_taps", c_int32)]
 
 
 class B2Sampling(ctypes.Structure):

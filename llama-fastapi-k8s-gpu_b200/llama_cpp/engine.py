@@ -292,7 +292,8 @@ class LayeredEngine(EngineBase):
         cfg = _cabi.B2LayeredConfig(dims.n_layer, dims.n_embd, dims.n_vocab, dims.norm_eps, dims.residual_scale, self.n_ctx,
                                     self.max_seqs, self.block_tokens, self.pages.num_blocks, self.max_step_tokens, self.device, flags,
                                     getattr(dims, "block_style", 0), getattr(dims, "logit_scale", 1.0), getattr(dims, "embed_scale", 1.0),
-                                    getattr(dims, "norm_groups", 1), 1 if getattr(dims, "tie_head", False) else 0)
+                                    getattr(dims, "norm_groups", 1), 1 if getattr(dims, "tie_head", False) else 0,
+                                    getattr(dims, "n_streams", 1), getattr(dims, "canon_taps", 0))
         descs = (_cabi.B2LayerDesc * dims.n_layer)(*dims.layers)
         h = ctypes.c_void_p()
         check(self.lib.b2_engine_create_layered(ctypes.byref(cfg), descs, ctypes.byref(h)), "b2_engine_create_layered")

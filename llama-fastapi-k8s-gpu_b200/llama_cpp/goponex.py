@@ -33,6 +33,8 @@ class LayeredDims:
     embed_scale: float = 1.0
     norm_groups: int = 1
     tie_head: bool = False
+    n_streams: int = 1
+    canon_taps: int = 0
 
 
 def _need(d: dict, key: str, where: str):

@@ -46,7 +46,7 @@ def architectures() -> List[str]:
 
 
 def _load_builtin():
-    from . import dibesun, goponex, llama_family, vazunex  # noqa: F401  (each registers itself on import)
+    from . import dibesun, goponex, llama_family, nafelix, vazunex  # noqa: F401  (each registers itself on import)
 
 
 def open_model(path: str) -> ModelSource:
