@@ -744,14 +744,75 @@ def dibesun_workload(args):
     return 0
 
 
+NAFELIX_SIZES = {      # name: (width, query heads of 128, expert ff; Vazunex heads and expert ff at equal width)
+    "1k": (1024, 8, 512, 8, 512),
+    "2k": (2048, 16, 1024, 16, 1024),
+    "4k": (4096, 32, 2048, 32, 2048),
+}
+
+
+def nafelix_workload(args):
+    """Prefill and decode throughput of the Nafelix layer-list graph at three layer sizes (random bf16 weights, four layers:
+    sink attention beside a head-decay delta rule, sink attention alone, and again; four copies of the stream, a 4-tap input
+    convolution; the first layer with a dense block, the others with a mixture of 16 clamped experts, 4 chosen) beside the
+    Vazunex graph (the closest existing model: the same engine, attention with a sink + matrix-state recurrences + expert
+    mixtures under pre-norm blocks) at equal width and depth. Device time with CUDA events around the engine calls."""
+    import numpy as np
+    from llama_cpp import nafelix, vazunex
+    hbm, hbm_src = measured_peak_gbs()
+    tfl, tfl_src = measured_peak_tflops()
+    n_prompt, n_dec, vocab = 2048, max(8, min(args.steps, 64)), 32000
+    rng = np.random.default_rng(0)
+    prompt = [int(t) for t in rng.integers(0, vocab, size=n_prompt)]
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    out, launches = {}, 0
+    warm = max(3, args.warmup // 4)
+    n_exp, top = 16, 4
+    for name in (args.sizes.split(",") if args.sizes else list(NAFELIX_SIZES)):
+        width, heads, ff, v_heads, v_eff = NAFELIX_SIZES[name]
+        cfg, tensors = nafelix.synthetic(width, heads, ff, vocab, experts=n_exp, top=top)
+        eng = nafelix.open_synthetic(cfg, tensors, n_ctx=n_prompt + 4 * n_dec + 64, max_seqs=4, dtype="bfloat16", max_step_tokens=n_prompt)
+        # a token passes through the shared matrices and `top` of the experts
+        n_expert = sum(int(np.prod(t.shape)) for k, t in tensors.items() if ".mlp.e" in k)
+        total = matrix_params(tensors)
+        n_param = total - n_expert + n_expert * top // n_exp
+        del tensors
+        rec, nl = time_layered(eng, prompt, n_dec, warm, n_param, tfl, hbm)
+        rec["matrix_params_total"] = total
+        launches += nl
+        eng.close()
+        cfg, tensors = vazunex.synthetic(width, v_heads, v_eff, vocab, experts=n_exp, top=top)
+        eng = vazunex.open_synthetic(cfg, tensors, n_ctx=n_prompt + 4 * n_dec + 64, max_seqs=4, dtype="bfloat16", max_step_tokens=n_prompt)
+        n_expert = sum(int(np.prod(t.shape)) for k, t in tensors.items() if ".mlp.e" in k)
+        v_param = matrix_params(tensors) - n_expert + n_expert * top // n_exp
+        del tensors
+        rec["vazunex"], nl = time_layered(eng, prompt, n_dec, warm, v_param, tfl, hbm)
+        eng.close()
+        out[name] = rec
+    clocks = sampler.result()
+    last = out[list(out)[-1]]
+    line = {"metric": "nafelix_prefill_tokens_per_s", "value": last["prefill_tok_s"], "unit": "tokens/s", "n_gpus": 1,
+            "steps": n_dec, "warmup": warm, "ms_per_step": last["decode_bs1_ms"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": "Nafelix layer-list graph, 4 layers (sink attention + head-decay delta rule, sink attention, twice; 4 stream copies, 4-tap input convolution; dense block, then 3 x 16 clamped experts, 4 chosen), random bf16 weights",
+                       "prompt_tokens": n_prompt, "decode_steps": n_dec, "global_batch": 1, "seq_len": n_prompt,
+                       "parallelism": "single GPU",
+                       "l2": "each step streams the weight set it uses (0.1-1 GB, larger than the 126 MB L2); no flush needed"},
+            "sizes": out, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tfl, "bf16_source": tfl_src},
+            "clocks": clocks, "gpu_launches": int(launches)}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="llama3-8b-q4_k_m-bs1", choices=sorted(WORKLOADS) + ["goponex-sizes", "vazunex-sizes", "dibesun-sizes"])
-    ap.add_argument("--sizes", default="", help="goponex-sizes / vazunex-sizes / dibesun-sizes: comma-separated subset of 1k,2k,4k (default all)")
+    ap.add_argument("--workload", default="llama3-8b-q4_k_m-bs1", choices=sorted(WORKLOADS) + ["goponex-sizes", "vazunex-sizes", "dibesun-sizes", "nafelix-sizes"])
+    ap.add_argument("--sizes", default="", help="goponex-sizes / vazunex-sizes / dibesun-sizes / nafelix-sizes: comma-separated subset of 1k,2k,4k (default all)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity-check", action="store_true")
     ap.add_argument("--batch-extra", type=int, default=32, help="bs1 workloads: also time this many sequences per step (0 = skip)")
@@ -761,12 +822,14 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.workload in ("goponex-sizes", "vazunex-sizes", "dibesun-sizes"):
+    if args.workload in ("goponex-sizes", "vazunex-sizes", "dibesun-sizes", "nafelix-sizes"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference has no layer-list models (llama.cpp graphs only)"}))
             return 0
         if args.workload == "dibesun-sizes":
             return dibesun_workload(args)
+        if args.workload == "nafelix-sizes":
+            return nafelix_workload(args)
         return goponex_workload(args) if args.workload == "goponex-sizes" else vazunex_workload(args)
     arch, ftype, n_prompt, batch = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))

@@ -276,7 +276,7 @@ int layered_finalize(b2_engine* e) {
     size_t moe_pairs = 0, moe_slots = 0, moe_ff = 0, moe_experts = 0, moe_xb = 0;     // moe_xb: expert activations per step token
     const bool hyper = c.block_style == B2_BLOCK_HYPER_RMS;
     const int n_streams = std::max(1, c.n_streams);
-    size_t max_cross = 0;
+    size_t max_cross = 0, max_part = 0;      // max_part: floats of one token's partial attention results with one key range
     // cache pages and recurrent state of a sink-attention layer (every run of a repeated layer has its own)
     auto sink_state = [&](LyLayer& L) -> int {
         const b2_layer_desc& d = L.d;
@@ -371,6 +371,7 @@ int layered_finalize(b2_engine* e) {
             max_proj = std::max<size_t>(max_proj, L.sk_proj.N);
             max_buf = std::max<size_t>({max_buf, (size_t)qd, (size_t)od, two ? (size_t)L.conv_C : 1, two ? (size_t)rvd : 1});
             if (d.attn_flags & B2_ATTN_TALK) max_cross = std::max<size_t>(max_cross, (size_t)H * G * d.attn_vdim);
+            max_part = std::max<size_t>(max_part, (size_t)H * ((d.attn_flags & B2_ATTN_TALK) ? G : 1) * (d.attn_vdim + 2));
         } else if (d.mixer == B2_MIX_WINDOW_SCAN) {
             const std::string a = p + "mix.left.", b = p + "mix.right.";
             const int qd = d.n_head * d.head_dim, kd = d.n_head_kv * d.head_dim;
@@ -575,7 +576,10 @@ int layered_finalize(b2_engine* e) {
     max_ff = std::max(max_ff, max_glu);
     if ((rc = dev_alloc(m, (void**)&m->ff, (size_t)Tm * max_ff * 4))) return rc;
     if (!m->exact && (rc = dev_alloc(m, (void**)&m->xb, (size_t)(Tm + B2_STEP_MAX_ENTRIES) * std::max<size_t>({max_buf, max_ff, (size_t)W, moe_xb}) * 2 + 64))) return rc;
-    if (max_attn > 0) {
+    if (max_part > 0) {                      // sink attention: up to 8 tokens x 16 key ranges
+        m->attn_split_floats = (int)std::min<size_t>(max_part * 8 * 16, (size_t)1 << 28);
+        if ((rc = dev_alloc(m, (void**)&m->attn_split, (size_t)m->attn_split_floats * 4))) return rc;
+    } else if (max_attn > 0) {
         m->attn_split_floats = (int)(148 * 2 * (max_attn_d + 2));       // T * H * splits <= 2 * 148 on the split path
         if ((rc = dev_alloc(m, (void**)&m->attn_split, (size_t)m->attn_split_floats * 4))) return rc;
     }
@@ -1045,6 +1049,7 @@ static int mix_sink(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& 
     a.H = H; a.G = d.n_head_kv; a.d = d.head_dim; a.dv = d.attn_vdim; a.window = d.window; a.scale = (float)d.attn_scale; a.eps = c.norm_eps;
     a.sink = L.sink; a.talk = L.talk; a.gate = m->proj + L.gl_off; a.ld_gate = Np; a.gate_per_head = (d.attn_flags & B2_ATTN_HEAD_GATE) ? 1 : 0;
     a.q_rot = m->buf[0]; a.cross = m->cross; a.out = m->buf[1]; a.ld_out = od;
+    a.part = m->attn_split; a.part_capacity = m->attn_split_floats; a.max_keys = d.window > 0 ? std::min(d.window, c.n_ctx) : c.n_ctx;
     {
         StepProfiler sp(m, st, 2);
         CK(sink_attn_store_launch(a, r, st));

@@ -306,6 +306,8 @@ struct SinkAttnArgs {
     const float* gate; int ld_gate; int gate_per_head;         // sigmoid output gate read at gate[t * ld_gate + (h | h * dv + i)], or null
     float* q_rot;                                              // scratch [T][H*d]
     float* cross;                                              // scratch [T][H][G][dv] (talk only)
+    float* part; int part_capacity;                            // few-token steps: (max, sum, output) per key range, floats available
+    int max_keys;                                              // most keys a query can see (the window, or the context size)
     float* out; int ld_out;                                    // out[t][h*dv + i]
 };
 // rotation (and unit RMS) of q and k, keys and values into the pages

@@ -82,34 +82,43 @@ cudaError_t sink_attn_store_launch(const SinkAttnArgs& a, const RaggedDev& r, cu
     return launch_chain(sink_attn_store_kernel, dim3(r.T), dim3(256), 0, s, a, r);
 }
 
-// grid (T, H, Gv), 8 warps. Query head h of token t against the keys of its own key head; the weights are applied to the values
-// of value head c = blockIdx.z when the heads' weights are mixed afterwards (Gv = G), else of the head's own (Gv = 1). A warp
-// takes 4 visible keys per round and keeps a running maximum, sum and output of its own; the warps are merged once, in warp
-// order, together with the sink term.
-constexpr int SK_WARPS = 8, SK_KEYS = 4;
+// grid (T, H * Gv, splits), 8 warps. Query head h of token t against the keys of its own key head; the weights are applied to the
+// values of value head c when the heads' weights are mixed afterwards (Gv = G), else of the head's own (Gv = 1). A warp takes 4
+// visible keys per round and keeps a running maximum, sum and output of its own; the warps are merged once, in warp order. With
+// one split the sink term joins there and the normalised result is written; with several (few-token steps: the visible keys are
+// cut into `splits` equal ranges so that a single decoded token still fills the GPU) every CTA leaves (maximum, sum, output) of
+// its range in `part` and sink_attn_merge_kernel adds them in range order.
+constexpr int SK_WARPS = 8, SK_KEYS = 4, SK_MAX_SPLITS = 16, SK_FEW_TOKENS = 8;
 template <bool F32>
 __global__ void __launch_bounds__(SK_WARPS * 32) sink_attn_kernel(SinkAttnArgs a, RaggedDev r) {
     griddep_launch();
     griddep_wait();
     __shared__ float sm_o[SK_WARPS][SK_MAXE * 32];
     __shared__ float sm_m[SK_WARPS], sm_l[SK_WARPS];
-    const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int Gv = a.talk ? a.G : 1;
+    const int t = blockIdx.x, h = blockIdx.y / Gv, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_splits = gridDim.z, split = blockIdx.z;
     const int pos = r.tok_pos[t];
     const int* table = a.block_tables[r.seg_slot[r.tok_seg[t]]];
     const int g = h / (a.H / a.G), d = a.d, dv = a.dv;
-    const int vg = a.talk ? (int)blockIdx.z : g;
+    const int vg = a.talk ? (int)(blockIdx.y % Gv) : g;
     const float* q = a.q_rot + ((size_t)t * a.H + h) * d;
     float qr[SK_MAXE], acc[SK_MAXE];
 #pragma unroll
     for (int e = 0; e < SK_MAXE; e++) { const int i = lane + 32 * e; qr[e] = i < d ? q[i] * a.scale : 0.f; acc[e] = 0.f; }
     float m_run = -INFINITY, l_run = 0.f;
-    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    for (int j0 = lo + warp * SK_KEYS; j0 <= pos; j0 += SK_WARPS * SK_KEYS) {
+    int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0, hi = pos;
+    if (n_splits > 1) {                                       // this CTA's share of the visible keys, whole warp rounds
+        const int per = ((pos - lo + n_splits) / n_splits + SK_WARPS * SK_KEYS - 1) / (SK_WARPS * SK_KEYS) * (SK_WARPS * SK_KEYS);
+        lo += split * per;
+        hi = min(pos, lo + per - 1);
+    }
+    for (int j0 = lo + warp * SK_KEYS; j0 <= hi; j0 += SK_WARPS * SK_KEYS) {
         size_t kb[SK_KEYS], vb[SK_KEYS];
         float sc[SK_KEYS];
 #pragma unroll
         for (int u = 0; u < SK_KEYS; u++) {
-            const int j = min(j0 + u, pos);                   // past the end: the last key again, its weight is dropped below
+            const int j = min(j0 + u, hi);                    // past the end: the last key again, its weight is dropped below
             const size_t page = table[j / a.block_tokens];
             kb[u] = ((page * a.G + g) * a.block_tokens + j % a.block_tokens) * d;
             vb[u] = ((page * a.G + vg) * a.block_tokens + j % a.block_tokens) * dv;
@@ -127,14 +136,14 @@ __global__ void __launch_bounds__(SK_WARPS * 32) sink_attn_kernel(SinkAttnArgs a
             for (int u = 0; u < SK_KEYS; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
         float mx = m_run;
 #pragma unroll
-        for (int u = 0; u < SK_KEYS; u++) if (j0 + u <= pos) mx = fmaxf(mx, sc[u]);
+        for (int u = 0; u < SK_KEYS; u++) if (j0 + u <= hi) mx = fmaxf(mx, sc[u]);
         const float corr = expf(m_run - mx);                  // 0 at the first round (m_run = -inf, mx finite)
         l_run *= corr;
 #pragma unroll
         for (int e = 0; e < SK_MAXE; e++) acc[e] *= corr;
 #pragma unroll
         for (int u = 0; u < SK_KEYS; u++) {
-            const float p = j0 + u <= pos ? expf(sc[u] - mx) : 0.f;
+            const float p = j0 + u <= hi ? expf(sc[u] - mx) : 0.f;
             l_run += p;
 #pragma unroll
             for (int e = 0; e < SK_MAXE; e++) { const int i = lane + 32 * e; if (i < dv) acc[e] = fmaf(p, sk_load<F32>(a.v_pool, vb[u] + i), acc[e]); }
@@ -145,19 +154,62 @@ __global__ void __launch_bounds__(SK_WARPS * 32) sink_attn_kernel(SinkAttnArgs a
     for (int e = 0; e < SK_MAXE; e++) sm_o[warp][lane + 32 * e] = acc[e];
     if (lane == 0) { sm_m[warp] = m_run; sm_l[warp] = l_run; }
     __syncthreads();
-    const float sink = a.sink ? a.sink[h] : -INFINITY;
+    const float sink = a.sink && n_splits == 1 ? a.sink[h] : -INFINITY;
     float m = sink;
 #pragma unroll
     for (int w2 = 0; w2 < SK_WARPS; w2++) m = fmaxf(m, sm_m[w2]);
-    float l = a.sink ? expf(sink - m) : 0.f;
+    float l = sink > -INFINITY ? expf(sink - m) : 0.f;
     float f[SK_WARPS];
 #pragma unroll
     for (int w2 = 0; w2 < SK_WARPS; w2++) { f[w2] = sm_m[w2] > -INFINITY ? expf(sm_m[w2] - m) : 0.f; l = fmaf(sm_l[w2], f[w2], l); }
+    if (n_splits > 1) {
+        float* part = a.part + ((((size_t)t * a.H + h) * Gv + (a.talk ? vg : 0)) * n_splits + split) * (dv + 2);
+        if (threadIdx.x == 0) { part[0] = m; part[1] = l; }
+        for (int i = threadIdx.x; i < dv; i += blockDim.x) {
+            float o = 0.f;
+#pragma unroll
+            for (int w2 = 0; w2 < SK_WARPS; w2++) o = fmaf(sm_o[w2][i], f[w2], o);
+            part[2 + i] = o;
+        }
+        return;
+    }
     const float inv = 1.f / l;
     for (int i = threadIdx.x; i < dv; i += blockDim.x) {
         float o = 0.f;
 #pragma unroll
         for (int w2 = 0; w2 < SK_WARPS; w2++) o = fmaf(sm_o[w2][i], f[w2], o);
+        o *= inv;
+        if (a.talk) a.cross[(((size_t)t * a.H + h) * a.G + vg) * dv + i] = o;
+        else a.out[(size_t)t * a.ld_out + (size_t)h * dv + i] = o * sk_gate(a, t, h, i);
+    }
+}
+
+// grid (T, H * Gv), 128 threads: the ranges' (maximum, sum, output) and the sink term, in range order
+__global__ void __launch_bounds__(128) sink_attn_merge_kernel(SinkAttnArgs a, int n_splits) {
+    griddep_launch();
+    griddep_wait();
+    const int Gv = a.talk ? a.G : 1;
+    const int t = blockIdx.x, h = blockIdx.y / Gv, vg = blockIdx.y % Gv, dv = a.dv;
+    const float* part = a.part + (((size_t)t * a.H + h) * Gv + vg) * n_splits * (dv + 2);
+    const float sink = a.sink ? a.sink[h] : -INFINITY;
+    float m = sink;
+    for (int s = 0; s < n_splits; s++) m = fmaxf(m, part[(size_t)s * (dv + 2)]);
+    float l = a.sink ? expf(sink - m) : 0.f;
+    float f[SK_MAX_SPLITS];
+#pragma unroll
+    for (int s = 0; s < SK_MAX_SPLITS; s++) {
+        f[s] = 0.f;
+        if (s < n_splits) {
+            const float ms = part[(size_t)s * (dv + 2)];
+            f[s] = ms > -INFINITY ? expf(ms - m) : 0.f;
+            l = fmaf(part[(size_t)s * (dv + 2) + 1], f[s], l);
+        }
+    }
+    const float inv = 1.f / l;
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
+        float o = 0.f;
+#pragma unroll
+        for (int s = 0; s < SK_MAX_SPLITS; s++) if (s < n_splits) o = fmaf(part[(size_t)s * (dv + 2) + 2 + i], f[s], o);
         o *= inv;
         if (a.talk) a.cross[(((size_t)t * a.H + h) * a.G + vg) * dv + i] = o;
         else a.out[(size_t)t * a.ld_out + (size_t)h * dv + i] = o * sk_gate(a, t, h, i);
@@ -177,11 +229,227 @@ __global__ void __launch_bounds__(256) sink_attn_talk_kernel(SinkAttnArgs a, int
     }
 }
 
+// Tensor-core prompt attention (bf16 pages, key and value sizes multiples of 16 up to 128): a CTA takes one tile of up to 64
+// consecutive queries of a segment, one query head and one value head; 4 warps x 16 query rows; keys in blocks of 64 from the block
+// that holds the oldest key of the tile's first query to the block of its last query, staged in shared memory once for all 64
+// queries. S = Q K^T and O += P V with mma.sync m16n8k16 (bf16 in, f32 accumulate); scale, mask, running maximum, sums and the
+// sink term are 32-bit. Queries and probabilities enter the products as TWO bf16 each (value = leading part + remainder), so the
+// only 16-bit rounding on this path is that of the cached keys and values -- the same as on the few-token path.
+constexpr int SKM_Q = 64, SKM_K = 64;
+namespace {
+__device__ __forceinline__ void sk_cp_async_16z(void* smem_dst, const void* gsrc, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void sk_ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void sk_ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void sk_mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void sk_split_bf16(float a, float b, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(a - __low2float(h), b - __high2float(h));
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+}  // namespace
+
+template <int DMAX, int DVMAX>
+__global__ void __launch_bounds__(128) sink_attn_mma_kernel(SinkAttnArgs a, RaggedDev r) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ __align__(16) unsigned char sk_smem[];
+    const int d = a.d, dv = a.dv, LD = d + 8, LDV = dv + 8;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(sk_smem);     // [64][LD] leading bf16 of the query
+    __nv_bfloat16* Ql = Qs + SKM_Q * LD;                                // [64][LD] what the first bf16 leaves over
+    __nv_bfloat16* Ks = Ql + SKM_Q * LD;                                // [64][LD]
+    __nv_bfloat16* Vs = Ks + SKM_K * LD;                                // [64][LDV]
+    const int Gv = a.talk ? a.G : 1;
+    // late tiles of a segment have the most key blocks: they start first
+    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y / Gv, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = r.tile_seg[tile], row0 = r.tile_row0[tile];
+    const int nq = min(SKM_Q, r.seg_start[seg] + r.seg_len[seg] - row0);
+    const int p0 = r.tok_pos[row0], p_last = p0 + nq - 1;
+    const int* table = a.block_tables[r.seg_slot[seg]];
+    const int g = h / (a.H / a.G);
+    const int vg = a.talk ? (int)(blockIdx.y % Gv) : g;
+    const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(a.k_pool);
+    const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(a.v_pool);
+    for (int i = threadIdx.x; i < SKM_Q * (d / 2); i += blockDim.x) {
+        const int rr = i / (d / 2), c = (i % (d / 2)) * 2;
+        float2 v = make_float2(0.f, 0.f);
+        if (rr < nq) v = *reinterpret_cast<const float2*>(a.q_rot + ((size_t)(row0 + rr) * a.H + h) * d + c);
+        v.x *= a.scale; v.y *= a.scale;
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(v.x, v.y);
+        *reinterpret_cast<__nv_bfloat162*>(Qs + rr * LD + c) = hi;
+        *reinterpret_cast<__nv_bfloat162*>(Ql + rr * LD + c) = __floats2bfloat162_rn(v.x - __low2float(hi), v.y - __high2float(hi));
+    }
+    const int lo_first = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
+    const int b0 = lo_first / SKM_K, b1 = p_last / SKM_K;
+    float o[DVMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DVMAX / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int qrow[2] = {warp * 16 + gq, warp * 16 + gq + 8};
+    int qlo[2];                                    // oldest visible key of the lane's two query rows
+    float m_run[2], l_run[2];
+    const float sink = a.sink ? a.sink[h] : -INFINITY;
+#pragma unroll
+    for (int q2 = 0; q2 < 2; q2++) {
+        const int i = p0 + qrow[q2];
+        qlo[q2] = a.window > 0 ? max(0, i - a.window + 1) : 0;
+        m_run[q2] = sink; l_run[q2] = 0.f;         // the running maximum starts at the sink; its term joins the sum at the end
+    }
+    for (int kb = b0; kb <= b1; kb++) {
+        const int j0 = kb * SKM_K;
+        __syncthreads();                      // everybody is done with the previous block's K and V (and Q is written)
+        for (int i = threadIdx.x; i < SKM_K * (d / 8); i += blockDim.x) {
+            const int rr = i / (d / 8), c = (i % (d / 8)) * 8;
+            const int j = j0 + rr, jj = min(j, p_last);
+            const size_t base = (((size_t)table[jj / a.block_tokens] * a.G + g) * a.block_tokens + jj % a.block_tokens) * d + c;
+            sk_cp_async_16z(Ks + rr * LD + c, kp + base, j <= p_last ? 16 : 0);
+        }
+        for (int i = threadIdx.x; i < SKM_K * (dv / 8); i += blockDim.x) {
+            const int rr = i / (dv / 8), c = (i % (dv / 8)) * 8;
+            const int j = j0 + rr, jj = min(j, p_last);
+            const size_t base = (((size_t)table[jj / a.block_tokens] * a.G + vg) * a.block_tokens + jj % a.block_tokens) * dv + c;
+            sk_cp_async_16z(Vs + rr * LDV + c, vp + base, j <= p_last ? 16 : 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        float sacc[SKM_K / 8][4];
+#pragma unroll
+        for (int ni = 0; ni < SKM_K / 8; ni++) sacc[ni][0] = sacc[ni][1] = sacc[ni][2] = sacc[ni][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < DMAX; ks += 16) {
+            if (ks < d) {
+                uint32_t af[4], al[4];
+                sk_ldsm_x4(af, Qs + (warp * 16 + (lane & 15)) * LD + ks + (lane >> 4) * 8);
+                sk_ldsm_x4(al, Ql + (warp * 16 + (lane & 15)) * LD + ks + (lane >> 4) * 8);
+#pragma unroll
+                for (int nj = 0; nj < SKM_K / 16; nj++) {
+                    uint32_t bf[4];
+                    sk_ldsm_x4(bf, Ks + (nj * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + ks + ((lane >> 3) & 1) * 8);
+                    sk_mma_16816(sacc[2 * nj], al, bf[0], bf[1]);
+                    sk_mma_16816(sacc[2 * nj + 1], al, bf[2], bf[3]);
+                    sk_mma_16816(sacc[2 * nj], af, bf[0], bf[1]);
+                    sk_mma_16816(sacc[2 * nj + 1], af, bf[2], bf[3]);
+                }
+            }
+        }
+        // mask, running maximum per query row (a row lives in the four lanes of a quad), probabilities
+        float mx[2] = {m_run[0], m_run[1]};
+#pragma unroll
+        for (int ni = 0; ni < SKM_K / 8; ni++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int rr = qrow[e >> 1], i = p0 + rr, j = j0 + ni * 8 + 2 * tq + (e & 1);
+                const bool vis = rr < nq && j <= i && j >= qlo[e >> 1];
+                sacc[ni][e] = vis ? sacc[ni][e] : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], sacc[ni][e]);
+            }
+        float corr[2], msafe[2], rs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int q2 = 0; q2 < 2; q2++) {
+            mx[q2] = fmaxf(mx[q2], __shfl_xor_sync(0xffffffffu, mx[q2], 1));
+            mx[q2] = fmaxf(mx[q2], __shfl_xor_sync(0xffffffffu, mx[q2], 2));
+            msafe[q2] = mx[q2] > -INFINITY ? mx[q2] : 0.f;             // nothing visible yet and no sink: every term is exp(-inf) = 0
+            corr[q2] = __expf(m_run[q2] - msafe[q2]);
+            m_run[q2] = mx[q2];
+        }
+#pragma unroll
+        for (int ni = 0; ni < SKM_K / 8; ni++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float p = __expf(sacc[ni][e] - msafe[e >> 1]);
+                sacc[ni][e] = p;
+                rs[e >> 1] += p;
+            }
+#pragma unroll
+        for (int q2 = 0; q2 < 2; q2++) {
+            rs[q2] += __shfl_xor_sync(0xffffffffu, rs[q2], 1);
+            rs[q2] += __shfl_xor_sync(0xffffffffu, rs[q2], 2);
+            l_run[q2] = fmaf(l_run[q2], corr[q2], rs[q2]);
+        }
+#pragma unroll
+        for (int i = 0; i < DVMAX / 8; i++) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+#pragma unroll
+        for (int kc = 0; kc < SKM_K / 16; kc++) {
+            uint32_t pf[4], pl[4];
+            sk_split_bf16(sacc[2 * kc][0], sacc[2 * kc][1], pf[0], pl[0]);
+            sk_split_bf16(sacc[2 * kc][2], sacc[2 * kc][3], pf[1], pl[1]);
+            sk_split_bf16(sacc[2 * kc + 1][0], sacc[2 * kc + 1][1], pf[2], pl[2]);
+            sk_split_bf16(sacc[2 * kc + 1][2], sacc[2 * kc + 1][3], pf[3], pl[3]);
+#pragma unroll
+            for (int nd = 0; nd < DVMAX / 16; nd++) {
+                if (nd * 16 < dv) {
+                    uint32_t vf[4];
+                    sk_ldsm_x4_t(vf, Vs + (kc * 16 + (lane & 15)) * LDV + nd * 16 + (lane >> 4) * 8);
+                    sk_mma_16816(o[2 * nd], pl, vf[0], vf[1]);
+                    sk_mma_16816(o[2 * nd + 1], pl, vf[2], vf[3]);
+                    sk_mma_16816(o[2 * nd], pf, vf[0], vf[1]);
+                    sk_mma_16816(o[2 * nd + 1], pf, vf[2], vf[3]);
+                }
+            }
+        }
+    }
+    float inv[2];
+#pragma unroll
+    for (int q2 = 0; q2 < 2; q2++) {
+        const float l = l_run[q2] + (a.sink ? __expf(sink - m_run[q2]) : 0.f);
+        inv[q2] = l > 0.f ? 1.f / l : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < DVMAX / 8; i++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int rr = qrow[e >> 1], c = i * 8 + 2 * tq + (e & 1);
+            if (rr >= nq || c >= dv) continue;
+            const float v = o[i][e] * inv[e >> 1];
+            const int t = row0 + rr;
+            if (a.talk) a.cross[(((size_t)t * a.H + h) * a.G + vg) * dv + c] = v;
+            else a.out[(size_t)t * a.ld_out + (size_t)h * dv + c] = v * sk_gate(a, t, h, c);
+        }
+}
+
+template <int DMAX, int DVMAX>
+static cudaError_t sink_attn_mma_pick(const SinkAttnArgs& a, const RaggedDev& r, cudaStream_t s) {
+    const size_t smem = (size_t)(3 * 64 * (a.d + 8) + 64 * (a.dv + 8)) * 2;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(sink_attn_mma_kernel<DMAX, DVMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (3 * 64 * (DMAX + 8) + 64 * (DVMAX + 8)) * 2);
+        attr_done = true;
+    }
+    return launch_chain(sink_attn_mma_kernel<DMAX, DVMAX>, dim3(r.n_tiles, a.H * (a.talk ? a.G : 1)), dim3(128), smem, s, a, r);
+}
+
 cudaError_t sink_attn_launch(const SinkAttnArgs& a, const RaggedDev& r, cudaStream_t s) {
     if (a.d > SK_MAXE * 32 || a.dv > SK_MAXE * 32 || a.H % a.G) return cudaErrorInvalidValue;
-    const dim3 grid(r.T, a.H, a.talk ? a.G : 1);
-    cudaError_t e = a.cache_f32 ? launch_chain(sink_attn_kernel<true>, grid, dim3(SK_WARPS * 32), 0, s, a, r)
-                                : launch_chain(sink_attn_kernel<false>, grid, dim3(SK_WARPS * 32), 0, s, a, r);
+    static const bool no_mma = getenv("B2_NO_ATTN_MMA") != nullptr;        // tuning aid: scalar attention for prompts too
+    const int Gv = a.talk ? a.G : 1;
+    cudaError_t e;
+    if (!no_mma && !a.cache_f32 && r.T > SK_FEW_TOKENS && a.d % 16 == 0 && a.dv % 16 == 0 && a.d <= 128 && a.dv <= 128) {
+        if (a.d <= 64) e = a.dv <= 64 ? sink_attn_mma_pick<64, 64>(a, r, s) : sink_attn_mma_pick<64, 128>(a, r, s);
+        else e = a.dv <= 64 ? sink_attn_mma_pick<128, 64>(a, r, s) : sink_attn_mma_pick<128, 128>(a, r, s);
+    } else {
+        // few tokens: enough key ranges to fill the GPU; the count depends on the step's shape and the window only, never on the
+        // positions, so that a captured step can be replayed
+        int splits = 1;
+        if (r.T <= SK_FEW_TOKENS && a.part) {
+            const int ctas = r.T * a.H * Gv;
+            splits = std::min({SK_MAX_SPLITS, std::max(1, (a.max_keys + 127) / 128), std::max(1, 592 / ctas)});
+            while (splits > 1 && (size_t)ctas * splits * (a.dv + 2) > (size_t)a.part_capacity) splits--;
+        }
+        const dim3 grid(r.T, a.H * Gv, splits);
+        e = a.cache_f32 ? launch_chain(sink_attn_kernel<true>, grid, dim3(SK_WARPS * 32), 0, s, a, r)
+                        : launch_chain(sink_attn_kernel<false>, grid, dim3(SK_WARPS * 32), 0, s, a, r);
+        if (e == cudaSuccess && splits > 1) e = launch_chain(sink_attn_merge_kernel, dim3(r.T, a.H * Gv), dim3(128), 0, s, a, splits);
+    }
     if (e != cudaSuccess || !a.talk) return e;
     return launch_chain(sink_attn_talk_kernel, dim3(r.T), dim3(256), 0, s, a, r.T);
 }
