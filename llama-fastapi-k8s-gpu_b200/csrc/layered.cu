@@ -1222,47 +1222,48 @@ static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
         HyperJoinArgs hj = {};
         MoeJoinArgs hj_moe = {};
         bool first = true;
-        auto boundary = [&](const float* in_w, const float* norm_w, float* hn, float* sum_out) -> int {
+        // cw / cstate: the convolution around a skip on the input that is read (null: none). Returns what the sublayer reads.
+        auto boundary = [&](const float* in_w, const float* norm_w, float* hn, float* sum_out, const float* cw, float* cstate, const float** in_out) -> int {
             StepProfiler sp(m, st, 5);
             hj.xs = m->xs; hj.stream_stride = (long)c.max_step_tokens * W; hj.S = std::max(1, c.n_streams); hj.eps = c.norm_eps;
             hj.in = in_w; hj.norm_w = norm_w; hj.hn = hn; hj.sum_out = sum_out; hj.bcast = first ? 1 : 0;
             hj.moe = hj_moe.sel ? &hj_moe : nullptr;
-            CK(hyper_join_launch(hj, W, T, st));
-            e->launches++;
+            ConvArgs cv = {};
+            cv.in = m->hn; cv.ld_in = W; cv.C = W; cv.taps = c.canon_taps; cv.w = cw; cv.state = cstate; cv.out = m->hc; cv.ld_out = W; cv.skip = 1;
+            if (hn && cw && hyper_join_conv_fits(W, c.canon_taps, T)) {
+                CK(hyper_join_conv_launch(hj, cv, r, W, st));
+                e->launches++;
+            } else {
+                CK(hyper_join_launch(hj, W, T, st));
+                e->launches++;
+                if (hn && cw) {
+                    CK(causal_conv_launch(cv, r, st));
+                    CK(causal_conv_advance_launch(cv, r, st));
+                    e->launches += c.canon_taps > 1 ? 2 : 1;
+                }
+            }
+            if (in_out) *in_out = hn && cw ? m->hc : m->hn;
             hj = HyperJoinArgs{}; hj_moe = MoeJoinArgs{};
             first = false;
             return B2_OK;
-        };
-        // the convolution around a skip on a sublayer's normed input; returns what the sublayer reads
-        auto canon = [&](LyLayer& L, int q) -> const float* {
-            if (!L.canon_w[q]) return m->hn;
-            ConvArgs cv = {};
-            cv.in = m->hn; cv.ld_in = W; cv.C = W; cv.taps = c.canon_taps; cv.w = L.canon_w[q]; cv.state = L.canon_state[q];
-            cv.out = m->hc; cv.ld_out = W; cv.skip = 1;
-            StepProfiler sp(m, st, 5);
-            if (causal_conv_launch(cv, r, st) != cudaSuccess || causal_conv_advance_launch(cv, r, st) != cudaSuccess) return nullptr;
-            e->launches += c.canon_taps > 1 ? 2 : 1;
-            return m->hc;
         };
         CK(cudaMemcpyAsync(m->xs, m->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
         for (int li = 0; li < c.n_layer; li++) {
             LyLayer& L = m->layers[li];
             const b2_layer_desc& d = L.d;
-            if ((rc = boundary(L.hc_in[0], L.norm1, m->hn, nullptr))) return rc;
-            const float* in = canon(L, 0);
-            if (!in) return b2_fail(B2_ERR_CUDA, "input convolution launch failed");
+            const float* in = nullptr;
+            if ((rc = boundary(L.hc_in[0], L.norm1, m->hn, nullptr, L.canon_w[0], L.canon_state[0], &in))) return rc;
             if ((rc = run_mixer(e, m, L, r, in))) return rc;
             hj.a = m->oL; hj.mix = L.hc_mix[0]; hj.out = L.hc_out[0];
             if (d.mixer == B2_MIX_SINK_DELTA) { hj.wa = L.left_w; hj.b = m->oR; hj.wb = L.right_w; }
             if (d.n_ff > 0) {
-                if ((rc = boundary(L.hc_in[1], L.norm2, m->hn, nullptr))) return rc;
-                if (!(in = canon(L, 1))) return b2_fail(B2_ERR_CUDA, "input convolution launch failed");
+                if ((rc = boundary(L.hc_in[1], L.norm2, m->hn, nullptr, L.canon_w[1], L.canon_state[1], &in))) return rc;
                 const bool moe = d.ff_kind == B2_FF_MOE;
                 if ((rc = run_ff(e, m, L, r, in, moe ? &hj_moe : nullptr))) return rc;
                 hj.a = moe ? nullptr : m->oL; hj.mix = L.hc_mix[1]; hj.out = L.hc_out[1];
             }
             if (m->trace || li == c.n_layer - 1) {
-                if ((rc = boundary(nullptr, nullptr, nullptr, m->x))) return rc;
+                if ((rc = boundary(nullptr, nullptr, nullptr, m->x, nullptr, nullptr, nullptr))) return rc;
                 if (m->trace) CK(cudaMemcpyAsync(m->trace + ((size_t)li * c.max_step_tokens) * W, m->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
             }
         }

@@ -82,30 +82,36 @@ cudaError_t sink_attn_store_launch(const SinkAttnArgs& a, const RaggedDev& r, cu
     return launch_chain(sink_attn_store_kernel, dim3(r.T), dim3(256), 0, s, a, r);
 }
 
-// grid (T, H * Gv, splits), 8 warps. Query head h of token t against the keys of its own key head; the weights are applied to the
-// values of value head c when the heads' weights are mixed afterwards (Gv = G), else of the head's own (Gv = 1). A warp takes 4
-// visible keys per round and keeps a running maximum, sum and output of its own; the warps are merged once, in warp order. With
+// grid (T, H * Gc, splits), 8 warps. Query head h of token t against the keys of its own key head; the weights are applied to the
+// values of the head's own key/value head (VH = 1, Gc = 1) or, when the heads' weights are mixed afterwards, to the values of VH
+// value heads at once (Gc = ceil(G / VH) chunks of value heads): the scores are computed once for all of them. A warp takes 4
+// visible keys per round and keeps a running maximum, sum and outputs of its own; the warps are merged once, in warp order. With
 // one split the sink term joins there and the normalised result is written; with several (few-token steps: the visible keys are
 // cut into `splits` equal ranges so that a single decoded token still fills the GPU) every CTA leaves (maximum, sum, output) of
 // its range in `part` and sink_attn_merge_kernel adds them in range order.
-constexpr int SK_WARPS = 8, SK_KEYS = 4, SK_MAX_SPLITS = 16, SK_FEW_TOKENS = 8;
-template <bool F32>
+constexpr int SK_WARPS = 8, SK_KEYS = 4, SK_MAX_SPLITS = 16, SK_FEW_TOKENS = 8, SK_VH = 4;
+template <bool F32, int VH>
 __global__ void __launch_bounds__(SK_WARPS * 32) sink_attn_kernel(SinkAttnArgs a, RaggedDev r) {
     griddep_launch();
     griddep_wait();
-    __shared__ float sm_o[SK_WARPS][SK_MAXE * 32];
+    extern __shared__ float sk_sm_o[];                        // [SK_WARPS][VH][SK_MAXE * 32]
     __shared__ float sm_m[SK_WARPS], sm_l[SK_WARPS];
-    const int Gv = a.talk ? a.G : 1;
-    const int t = blockIdx.x, h = blockIdx.y / Gv, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int Gv = a.talk ? a.G : 1, Gc = (Gv + VH - 1) / VH;
+    const int t = blockIdx.x, h = blockIdx.y / Gc, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_splits = gridDim.z, split = blockIdx.z;
     const int pos = r.tok_pos[t];
     const int* table = a.block_tables[r.seg_slot[r.tok_seg[t]]];
     const int g = h / (a.H / a.G), d = a.d, dv = a.dv;
-    const int vg = a.talk ? (int)(blockIdx.y % Gv) : g;
+    const int vg0 = a.talk ? (int)(blockIdx.y % Gc) * VH : g;            // first of this CTA's value heads
     const float* q = a.q_rot + ((size_t)t * a.H + h) * d;
-    float qr[SK_MAXE], acc[SK_MAXE];
+    float qr[SK_MAXE], acc[VH][SK_MAXE];
 #pragma unroll
-    for (int e = 0; e < SK_MAXE; e++) { const int i = lane + 32 * e; qr[e] = i < d ? q[i] * a.scale : 0.f; acc[e] = 0.f; }
+    for (int e = 0; e < SK_MAXE; e++) {
+        const int i = lane + 32 * e;
+        qr[e] = i < d ? q[i] * a.scale : 0.f;
+#pragma unroll
+        for (int v = 0; v < VH; v++) acc[v][e] = 0.f;
+    }
     float m_run = -INFINITY, l_run = 0.f;
     int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0, hi = pos;
     if (n_splits > 1) {                                       // this CTA's share of the visible keys, whole warp rounds
@@ -121,7 +127,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) sink_attn_kernel(SinkAttnArgs a
             const int j = min(j0 + u, hi);                    // past the end: the last key again, its weight is dropped below
             const size_t page = table[j / a.block_tokens];
             kb[u] = ((page * a.G + g) * a.block_tokens + j % a.block_tokens) * d;
-            vb[u] = ((page * a.G + vg) * a.block_tokens + j % a.block_tokens) * dv;
+            vb[u] = (page * a.G * a.block_tokens + j % a.block_tokens) * dv;       // value head v adds v * block_tokens * dv
         }
 #pragma unroll
         for (int u = 0; u < SK_KEYS; u++) {
@@ -140,18 +146,26 @@ __global__ void __launch_bounds__(SK_WARPS * 32) sink_attn_kernel(SinkAttnArgs a
         const float corr = expf(m_run - mx);                  // 0 at the first round (m_run = -inf, mx finite)
         l_run *= corr;
 #pragma unroll
-        for (int e = 0; e < SK_MAXE; e++) acc[e] *= corr;
+        for (int v = 0; v < VH; v++)
+#pragma unroll
+            for (int e = 0; e < SK_MAXE; e++) acc[v][e] *= corr;
 #pragma unroll
         for (int u = 0; u < SK_KEYS; u++) {
             const float p = j0 + u <= hi ? expf(sc[u] - mx) : 0.f;
             l_run += p;
 #pragma unroll
-            for (int e = 0; e < SK_MAXE; e++) { const int i = lane + 32 * e; if (i < dv) acc[e] = fmaf(p, sk_load<F32>(a.v_pool, vb[u] + i), acc[e]); }
+            for (int v = 0; v < VH; v++) {
+                const size_t vbase = vb[u] + (size_t)min(vg0 + v, a.G - 1) * a.block_tokens * dv;       // past the last head: its last one again, not stored
+#pragma unroll
+                for (int e = 0; e < SK_MAXE; e++) { const int i = lane + 32 * e; if (i < dv) acc[v][e] = fmaf(p, sk_load<F32>(a.v_pool, vbase + i), acc[v][e]); }
+            }
         }
         m_run = mx;
     }
 #pragma unroll
-    for (int e = 0; e < SK_MAXE; e++) sm_o[warp][lane + 32 * e] = acc[e];
+    for (int v = 0; v < VH; v++)
+#pragma unroll
+        for (int e = 0; e < SK_MAXE; e++) sk_sm_o[(warp * VH + v) * (SK_MAXE * 32) + lane + 32 * e] = acc[v][e];
     if (lane == 0) { sm_m[warp] = m_run; sm_l[warp] = l_run; }
     __syncthreads();
     const float sink = a.sink && n_splits == 1 ? a.sink[h] : -INFINITY;
@@ -162,24 +176,19 @@ __global__ void __launch_bounds__(SK_WARPS * 32) sink_attn_kernel(SinkAttnArgs a
     float f[SK_WARPS];
 #pragma unroll
     for (int w2 = 0; w2 < SK_WARPS; w2++) { f[w2] = sm_m[w2] > -INFINITY ? expf(sm_m[w2] - m) : 0.f; l = fmaf(sm_l[w2], f[w2], l); }
-    if (n_splits > 1) {
-        float* part = a.part + ((((size_t)t * a.H + h) * Gv + (a.talk ? vg : 0)) * n_splits + split) * (dv + 2);
-        if (threadIdx.x == 0) { part[0] = m; part[1] = l; }
-        for (int i = threadIdx.x; i < dv; i += blockDim.x) {
-            float o = 0.f;
-#pragma unroll
-            for (int w2 = 0; w2 < SK_WARPS; w2++) o = fmaf(sm_o[w2][i], f[w2], o);
-            part[2 + i] = o;
-        }
-        return;
-    }
-    const float inv = 1.f / l;
-    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
+    const float inv = n_splits > 1 ? 1.f : 1.f / l;
+    for (int e = threadIdx.x; e < VH * dv; e += blockDim.x) {
+        const int v = e / dv, i = e - v * dv, vg = vg0 + v;
+        if (a.talk && vg >= a.G) continue;
         float o = 0.f;
 #pragma unroll
-        for (int w2 = 0; w2 < SK_WARPS; w2++) o = fmaf(sm_o[w2][i], f[w2], o);
+        for (int w2 = 0; w2 < SK_WARPS; w2++) o = fmaf(sk_sm_o[(w2 * VH + v) * (SK_MAXE * 32) + i], f[w2], o);
         o *= inv;
-        if (a.talk) a.cross[(((size_t)t * a.H + h) * a.G + vg) * dv + i] = o;
+        if (n_splits > 1) {
+            float* part = a.part + ((((size_t)t * a.H + h) * Gv + (a.talk ? vg : 0)) * n_splits + split) * (dv + 2);
+            if (i == 0) { part[0] = m; part[1] = l; }
+            part[2 + i] = o;
+        } else if (a.talk) a.cross[(((size_t)t * a.H + h) * a.G + vg) * dv + i] = o;
         else a.out[(size_t)t * a.ld_out + (size_t)h * dv + i] = o * sk_gate(a, t, h, i);
     }
 }
@@ -216,16 +225,15 @@ __global__ void __launch_bounds__(128) sink_attn_merge_kernel(SinkAttnArgs a, in
     }
 }
 
-// grid (T): out_h = gate_h * sum_g talk[h][g] A[g][c(h)], the sum in head order
-__global__ void __launch_bounds__(256) sink_attn_talk_kernel(SinkAttnArgs a, int T) {
+// grid (T, H), 128 threads: out_h = gate_h * sum_g talk[h][g] A[g][c(h)], the sum in head order
+__global__ void __launch_bounds__(128) sink_attn_talk_kernel(SinkAttnArgs a, int T) {
     griddep_launch();
     griddep_wait();
-    const int t = blockIdx.x, H = a.H, G = a.G, dv = a.dv;
-    for (int e = threadIdx.x; e < H * dv; e += blockDim.x) {
-        const int h = e / dv, i = e - h * dv, c = h / (H / G);
+    const int t = blockIdx.x, h = blockIdx.y, H = a.H, G = a.G, dv = a.dv, c = h / (H / G);
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
         float o = 0.f;
         for (int g = 0; g < H; g++) o = fmaf(a.talk[h * H + g], a.cross[(((size_t)t * H + g) * G + c) * dv + i], o);
-        a.out[(size_t)t * a.ld_out + e] = o * sk_gate(a, t, h, i);
+        a.out[(size_t)t * a.ld_out + (size_t)h * dv + i] = o * sk_gate(a, t, h, i);
     }
 }
 
@@ -441,17 +449,25 @@ cudaError_t sink_attn_launch(const SinkAttnArgs& a, const RaggedDev& r, cudaStre
         // positions, so that a captured step can be replayed
         int splits = 1;
         if (r.T <= SK_FEW_TOKENS && a.part) {
-            const int ctas = r.T * a.H * Gv;
+            const int ctas = r.T * a.H * (a.talk ? (a.G + SK_VH - 1) / SK_VH : 1);
             splits = std::min({SK_MAX_SPLITS, std::max(1, (a.max_keys + 127) / 128), std::max(1, 592 / ctas)});
-            while (splits > 1 && (size_t)ctas * splits * (a.dv + 2) > (size_t)a.part_capacity) splits--;
+            while (splits > 1 && (size_t)r.T * a.H * Gv * splits * (a.dv + 2) > (size_t)a.part_capacity) splits--;
         }
-        const dim3 grid(r.T, a.H * Gv, splits);
-        e = a.cache_f32 ? launch_chain(sink_attn_kernel<true>, grid, dim3(SK_WARPS * 32), 0, s, a, r)
-                        : launch_chain(sink_attn_kernel<false>, grid, dim3(SK_WARPS * 32), 0, s, a, r);
+        if (a.talk) {
+            const dim3 grid(r.T, a.H * ((a.G + SK_VH - 1) / SK_VH), splits);
+            const size_t smem = (size_t)SK_WARPS * SK_VH * SK_MAXE * 32 * 4;
+            e = a.cache_f32 ? launch_chain(sink_attn_kernel<true, SK_VH>, grid, dim3(SK_WARPS * 32), smem, s, a, r)
+                            : launch_chain(sink_attn_kernel<false, SK_VH>, grid, dim3(SK_WARPS * 32), smem, s, a, r);
+        } else {
+            const dim3 grid(r.T, a.H, splits);
+            const size_t smem = (size_t)SK_WARPS * SK_MAXE * 32 * 4;
+            e = a.cache_f32 ? launch_chain(sink_attn_kernel<true, 1>, grid, dim3(SK_WARPS * 32), smem, s, a, r)
+                            : launch_chain(sink_attn_kernel<false, 1>, grid, dim3(SK_WARPS * 32), smem, s, a, r);
+        }
         if (e == cudaSuccess && splits > 1) e = launch_chain(sink_attn_merge_kernel, dim3(r.T, a.H * Gv), dim3(128), 0, s, a, splits);
     }
     if (e != cudaSuccess || !a.talk) return e;
-    return launch_chain(sink_attn_talk_kernel, dim3(r.T), dim3(256), 0, s, a, r.T);
+    return launch_chain(sink_attn_talk_kernel, dim3(r.T, a.H), dim3(128), 0, s, a, r.T);
 }
 
 }  // namespace b2
