@@ -7,7 +7,7 @@
 
 namespace b2 {
 
-constexpr int HY_MAX_S = 8;
+constexpr int HY_MAX_S = 16;       // copies of the stream; the kernels are compiled for up to 4, 8 and 16
 
 namespace {
 struct HyperDev {
@@ -33,6 +33,7 @@ __device__ __forceinline__ float hy_block_sum(float v, float* red) {      // all
 
 // one token: write the pending output back, sum the copies, read the next sublayer's input. With `row` (shared, [W]) the normed
 // input is left there for the caller (all threads have passed a barrier after the last write); else it goes to a.hn.
+template <int SM>
 __device__ __forceinline__ void hyper_token(const HyperDev& p, int t, float* hy_row, float* red, const float* s_mix, const float* s_out,
                                             const float* s_in, bool keep_in_row) {
     const HyperJoinArgs& a = p.a;
@@ -49,9 +50,9 @@ __device__ __forceinline__ void hyper_token(const HyperDev& p, int t, float* hy_
     }
     float ss = 0.f;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        float x[HY_MAX_S];
+        float x[SM];
 #pragma unroll
-        for (int s = 0; s < HY_MAX_S; s++) if (s < S) x[s] = a.xs[(a.bcast ? 0 : s) * a.stream_stride + base + i];
+        for (int s = 0; s < SM; s++) if (s < S) x[s] = a.xs[(a.bcast ? 0 : s) * a.stream_stride + base + i];
         if (pending) {
             float y = 0.f;
             if (a.b) y = 0.5f * (a.a[base + i] * ra * a.wa[i] + a.b[base + i] * rb * a.wb[i]);
@@ -64,32 +65,32 @@ __device__ __forceinline__ void hyper_token(const HyperDev& p, int t, float* hy_
                     y = fmaf(j.weight[q], v, y);
                 }
             }
-            float nx[HY_MAX_S];
+            float nx[SM];
 #pragma unroll
-            for (int to = 0; to < HY_MAX_S; to++) {
+            for (int to = 0; to < SM; to++) {
                 if (to >= S) continue;
                 float v = s_out[to] * y;
 #pragma unroll
-                for (int s = 0; s < HY_MAX_S; s++) if (s < S) v = fmaf(s_mix[s * S + to], x[s], v);
+                for (int s = 0; s < SM; s++) if (s < S) v = fmaf(s_mix[s * S + to], x[s], v);
                 nx[to] = v;
             }
 #pragma unroll
-            for (int s = 0; s < HY_MAX_S; s++) if (s < S) x[s] = nx[s];
+            for (int s = 0; s < SM; s++) if (s < S) x[s] = nx[s];
         }
         if (pending || a.bcast) {
 #pragma unroll
-            for (int s = 0; s < HY_MAX_S; s++) if (s < S && (pending || s > 0)) a.xs[s * a.stream_stride + base + i] = x[s];
+            for (int s = 0; s < SM; s++) if (s < S && (pending || s > 0)) a.xs[s * a.stream_stride + base + i] = x[s];
         }
         if (a.sum_out) {
             float v = 0.f;
 #pragma unroll
-            for (int s = 0; s < HY_MAX_S; s++) if (s < S) v += x[s];
+            for (int s = 0; s < SM; s++) if (s < S) v += x[s];
             a.sum_out[base + i] = v;
         }
         if (a.hn) {
             float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < HY_MAX_S; s++) if (s < S) u = fmaf(s_in[s], x[s], u);
+            for (int s = 0; s < SM; s++) if (s < S) u = fmaf(s_in[s], x[s], u);
             hy_row[i] = u;
             ss = fmaf(u, u, ss);
         }
@@ -113,7 +114,7 @@ __device__ __forceinline__ void hyper_tables(const HyperJoinArgs& a, float* s_mi
 
 // grid (T), NT threads (256 when the step has many tokens, 1024 when it has few: a decoded token's row is then walked in a quarter
 // of the rounds, and the kernel is bound by the latency of those rounds); shared: [W] the next sublayer's input before its norm
-template <int NT>
+template <int NT, int SM>
 __global__ void __launch_bounds__(NT) hyper_join_kernel(HyperDev p) {
     griddep_launch();
     griddep_wait();
@@ -121,13 +122,14 @@ __global__ void __launch_bounds__(NT) hyper_join_kernel(HyperDev p) {
     __shared__ float red[33];
     __shared__ float s_mix[HY_MAX_S * HY_MAX_S], s_out[HY_MAX_S], s_in[HY_MAX_S];
     hyper_tables(p.a, s_mix, s_out, s_in);
-    hyper_token(p, blockIdx.x, hy_row, red, s_mix, s_out, s_in, false);
+    hyper_token<SM>(p, blockIdx.x, hy_row, red, s_mix, s_out, s_in, false);
 }
 
 // Few-token steps: the same pass joined to the convolution around a skip on the sublayer's input and to the hand-over of its
 // state. grid (n_seg), 1024 threads: a CTA walks its segment's tokens in order; the normed inputs of the last `taps` tokens live
 // in a ring in shared memory ([taps][W]); older ones come from the slot's state, which is rewritten at the end. The sums run in
 // the order of causal_conv_kernel, so both paths give the same numbers.
+template <int SM>
 __global__ void __launch_bounds__(1024) hyper_join_conv_kernel(HyperDev p, ConvArgs cv, RaggedDev r) {
     griddep_launch();
     griddep_wait();
@@ -140,7 +142,7 @@ __global__ void __launch_bounds__(1024) hyper_join_conv_kernel(HyperDev p, ConvA
     float* state = cv.state + (size_t)slot * hist * W;
     for (int k = 0; k < len; k++) {
         float* row = hy_ring + (size_t)(k % taps) * W;
-        hyper_token(p, start + k, row, red, s_mix, s_out, s_in, true);
+        hyper_token<SM>(p, start + k, row, red, s_mix, s_out, s_in, true);
         for (int c = threadIdx.x; c < W; c += blockDim.x) {
             float acc = 0.f;
             for (int j = 0; j < taps; j++) {
@@ -159,6 +161,26 @@ __global__ void __launch_bounds__(1024) hyper_join_conv_kernel(HyperDev p, ConvA
         }
 }
 
+template <int SM>
+static cudaError_t hyper_join_pick(const HyperDev& p, bool few, int T, size_t smem, cudaStream_t s) {
+    if (smem > 48 * 1024) {
+        static bool attr_done = false;
+        if (!attr_done) {
+            cudaFuncSetAttribute(hyper_join_kernel<256, SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            cudaFuncSetAttribute(hyper_join_kernel<1024, SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            attr_done = true;
+        }
+    }
+    if (few && SM <= 8) return launch_chain(hyper_join_kernel<1024, SM>, dim3(T), dim3(1024), smem, s, p);
+    return launch_chain(hyper_join_kernel<256, SM>, dim3(T), dim3(256), smem, s, p);
+}
+template <int SM>
+static cudaError_t hyper_join_conv_pick(const HyperDev& p, const ConvArgs& cv, const RaggedDev& r, int W, size_t smem, cudaStream_t s) {
+    static bool attr_done = false;
+    if (!attr_done) { cudaFuncSetAttribute(hyper_join_conv_kernel<SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); attr_done = true; }
+    return launch_chain(hyper_join_conv_kernel<SM>, dim3(r.n_seg), dim3(W >= 1024 ? 1024 : 256), smem, s, p, cv, r);
+}
+
 cudaError_t hyper_join_launch(const HyperJoinArgs& a, int W, int T, cudaStream_t s) {
     if (a.S <= 0 || a.S > HY_MAX_S) return cudaErrorInvalidValue;
     HyperDev p = {};
@@ -166,19 +188,11 @@ cudaError_t hyper_join_launch(const HyperJoinArgs& a, int W, int T, cudaStream_t
     if (a.moe) { p.moe = *a.moe; p.moe_on = 1; }
     p.a.moe = nullptr;
     const size_t smem = (size_t)W * 4;
-    if (smem > 48 * 1024) {
-        static bool attr_done = false;
-        if (!attr_done) {
-            cudaFuncSetAttribute(hyper_join_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            cudaFuncSetAttribute(hyper_join_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            attr_done = true;
-        }
-    }
-    if (T <= 16 && W >= 1024) return launch_chain(hyper_join_kernel<1024>, dim3(T), dim3(1024), smem, s, p);
-    return launch_chain(hyper_join_kernel<256>, dim3(T), dim3(256), smem, s, p);
+    const bool few = T <= 16 && W >= 1024;
+    return a.S <= 4 ? hyper_join_pick<4>(p, few, T, smem, s) : a.S <= 8 ? hyper_join_pick<8>(p, few, T, smem, s) : hyper_join_pick<16>(p, few, T, smem, s);
 }
 
-bool hyper_join_conv_fits(int W, int taps, int T) { return T <= 8 && taps >= 1 && (size_t)taps * W * 4 <= 160 * 1024; }
+bool hyper_join_conv_fits(int W, int taps, int T, int S) { return T <= 8 && S <= 8 && taps >= 1 && (size_t)taps * W * 4 <= 160 * 1024; }
 
 cudaError_t hyper_join_conv_launch(const HyperJoinArgs& a, const ConvArgs& cv, const RaggedDev& r, int W, cudaStream_t s) {
     if (a.S <= 0 || a.S > HY_MAX_S || !a.hn || !cv.skip || cv.C != W || cv.ld_in != W) return cudaErrorInvalidValue;
@@ -187,9 +201,8 @@ cudaError_t hyper_join_conv_launch(const HyperJoinArgs& a, const ConvArgs& cv, c
     if (a.moe) { p.moe = *a.moe; p.moe_on = 1; }
     p.a.moe = nullptr;
     const size_t smem = (size_t)cv.taps * W * 4;
-    static bool attr_done = false;
-    if (!attr_done) { cudaFuncSetAttribute(hyper_join_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); attr_done = true; }
-    return launch_chain(hyper_join_conv_kernel, dim3(r.n_seg), dim3(W >= 1024 ? 1024 : 256), smem, s, p, cv, r);
+    if (a.S > 8) return cudaErrorInvalidValue;          // more copies take the separate kernels (hyper_join_conv_fits)
+    return a.S <= 4 ? hyper_join_conv_pick<4>(p, cv, r, W, smem, s) : hyper_join_conv_pick<8>(p, cv, r, W, smem, s);
 }
 
 }  // namespace b2

@@ -737,7 +737,7 @@ extern "C" int b2_engine_create_layered(const b2_layered_config* c, const b2_lay
         c->block_style != B2_BLOCK_HYPER_RMS)
         return b2_fail(B2_ERR_ARG, "unknown block style");
     if (c->block_style == B2_BLOCK_HYPER_RMS) {
-        if (c->n_streams < 0 || c->n_streams > 8) return b2_fail(B2_ERR_UNSUPPORTED, "at most 8 copies of the stream");
+        if (c->n_streams < 0 || c->n_streams > 16) return b2_fail(B2_ERR_UNSUPPORTED, "at most 16 copies of the stream");
         if (c->canon_taps < 0 || c->canon_taps > 64) return b2_fail(B2_ERR_ARG, "bad number of taps");
         for (int i = 0; i < c->n_layer; i++)
             if (layers[i].mixer != B2_MIX_SINK_DELTA && layers[i].mixer != B2_MIX_SINK_ATTN)
@@ -1230,7 +1230,7 @@ static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
             hj.moe = hj_moe.sel ? &hj_moe : nullptr;
             ConvArgs cv = {};
             cv.in = m->hn; cv.ld_in = W; cv.C = W; cv.taps = c.canon_taps; cv.w = cw; cv.state = cstate; cv.out = m->hc; cv.ld_out = W; cv.skip = 1;
-            if (hn && cw && hyper_join_conv_fits(W, c.canon_taps, T)) {
+            if (hn && cw && hyper_join_conv_fits(W, c.canon_taps, T, hj.S)) {
                 CK(hyper_join_conv_launch(hj, cv, r, W, st));
                 e->launches++;
             } else {

@@ -336,7 +336,7 @@ cudaError_t hyper_join_launch(const HyperJoinArgs& a, int W, int T, cudaStream_t
 // Few-token steps (hyper_join_conv_fits): the same pass, the convolution around a skip on the input it reads (cv.in is not used:
 // the normed input never leaves the chip; cv.out gets in + conv(in)) and the hand-over of the convolution's state, in ONE launch
 // with one CTA per segment. Same numbers as hyper_join_launch + causal_conv_launch + causal_conv_advance_launch.
-bool hyper_join_conv_fits(int W, int taps, int T);
+bool hyper_join_conv_fits(int W, int taps, int T, int S);
 cudaError_t hyper_join_conv_launch(const HyperJoinArgs& a, const ConvArgs& cv, const RaggedDev& r, int W, cudaStream_t s);
 
 // ---------------------------------------------------------------- graph (layered.cu)

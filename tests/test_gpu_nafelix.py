@@ -445,10 +445,10 @@ def test_sizes_that_are_one_odd_or_large(native_lib, tmp_path, dtype):
 @pytest.mark.parametrize("width", [45, 50])
 def test_widths_no_vector_path_takes(native_lib, tmp_path, width, dtype):
     """A model width that is odd, or even but no multiple of four: every product over the width takes its scalar path, in
-    prompts (tiles) and in few-token steps (rows); eight copies of the stream."""
+    prompts (tiles) and in few-token steps (rows); eight and eleven copies of the stream."""
     from llama_cpp.kv_pages import SequenceSlots
     cfg = nu.config([nu.parallel(mlp=nu.moe(experts=4, top=2, ff=10), left=nu.attn(heads=2, kv_heads=2, dim=12, vdim=10, window=40, rot=6)),
-                     nu.attention(mlp=nu.dense(13))], width=width, vocab=77, streams=8, taps=4)
+                     nu.attention(mlp=nu.dense(13))], width=width, vocab=77, streams=8 if width == 45 else 11, taps=4)
     w = nu.random_weights(cfg, seed=21)
     eng = open_engine(nu.write_model(str(tmp_path / "m"), cfg, w), dtype)
     toks = tokens_for(cfg, 150, 22)
