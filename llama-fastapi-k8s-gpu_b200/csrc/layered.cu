@@ -90,6 +90,8 @@ struct LayeredModel {
     float *moe_logits = nullptr, *moe_weight = nullptr, *moe_h = nullptr, *moe_y = nullptr;
     int *moe_sel = nullptr, *moe_tok = nullptr, *moe_pos = nullptr, *moe_rows = nullptr, *moe_tiles = nullptr;
     int moe_max_tiles = 0;
+    float* attn_pbuf = nullptr;        // prompts with mixed heads: normalised attention weights of a group of query tiles
+    size_t attn_pbuf_floats = 0;
     float* attn_split = nullptr;       // few-token steps: partial attention results per key range
     int attn_split_floats = 0;
     int* meta = nullptr;               // device ints: ragged description + wanted rows
@@ -276,7 +278,7 @@ int layered_finalize(b2_engine* e) {
     size_t moe_pairs = 0, moe_slots = 0, moe_ff = 0, moe_experts = 0, moe_xb = 0;     // moe_xb: expert activations per step token
     const bool hyper = c.block_style == B2_BLOCK_HYPER_RMS;
     const int n_streams = std::max(1, c.n_streams);
-    size_t max_cross = 0, max_part = 0;      // max_part: floats of one token's partial attention results with one key range
+    size_t max_cross = 0, max_pbuf = 0, max_part = 0;      // max_part: floats of one token's partial attention results with one key range
     // cache pages and recurrent state of a sink-attention layer (every run of a repeated layer has its own)
     auto sink_state = [&](LyLayer& L) -> int {
         const b2_layer_desc& d = L.d;
@@ -372,6 +374,10 @@ int layered_finalize(b2_engine* e) {
             max_buf = std::max<size_t>({max_buf, (size_t)qd, (size_t)od, two ? (size_t)L.conv_C : 1, two ? (size_t)rvd : 1});
             if (d.attn_flags & B2_ATTN_TALK) max_cross = std::max<size_t>(max_cross, (size_t)H * G * d.attn_vdim);
             max_part = std::max<size_t>(max_part, (size_t)H * ((d.attn_flags & B2_ATTN_TALK) ? G : 1) * (d.attn_vdim + 2));
+            if ((d.attn_flags & B2_ATTN_TALK) && !m->exact) {       // all tiles of the largest step, up to 512 MB
+                const size_t keys = d.window > 0 ? std::min(d.window, c.n_ctx) : c.n_ctx;
+                max_pbuf = std::max<size_t>(max_pbuf, (size_t)H * 64 * ((keys + 62) / 64 + 2) * 64 * (Tm / 64 + 2));
+            }
         } else if (d.mixer == B2_MIX_WINDOW_SCAN) {
             const std::string a = p + "mix.left.", b = p + "mix.right.";
             const int qd = d.n_head * d.head_dim, kd = d.n_head_kv * d.head_dim;
@@ -567,6 +573,10 @@ int layered_finalize(b2_engine* e) {
         if ((rc = dev_alloc(m, (void**)&m->xs, (size_t)n_streams * Tm * W * 4))) return rc;
         if ((rc = dev_alloc(m, (void**)&m->hc, (size_t)Tm * W * 4))) return rc;
         if (max_cross > 0 && (rc = dev_alloc(m, (void**)&m->cross, (size_t)Tm * max_cross * 4))) return rc;
+        if (max_pbuf > 0) {
+            m->attn_pbuf_floats = std::min<size_t>(max_pbuf, (size_t)128 << 20);
+            if ((rc = dev_alloc(m, (void**)&m->attn_pbuf, m->attn_pbuf_floats * 4))) return rc;
+        }
     }
     if ((rc = dev_alloc(m, (void**)&m->proj, (size_t)Tm * max_proj * 4))) return rc;
     for (int i = 0; i < 4; i++) if ((rc = dev_alloc(m, (void**)&m->buf[i], (size_t)Tm * max_buf * 4))) return rc;
@@ -1049,6 +1059,7 @@ static int mix_sink(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& 
     a.H = H; a.G = d.n_head_kv; a.d = d.head_dim; a.dv = d.attn_vdim; a.window = d.window; a.scale = (float)d.attn_scale; a.eps = c.norm_eps;
     a.sink = L.sink; a.talk = L.talk; a.gate = m->proj + L.gl_off; a.ld_gate = Np; a.gate_per_head = (d.attn_flags & B2_ATTN_HEAD_GATE) ? 1 : 0;
     a.q_rot = m->buf[0]; a.cross = m->cross; a.out = m->buf[1]; a.ld_out = od;
+    a.pbuf = m->attn_pbuf; a.pbuf_floats = m->attn_pbuf_floats;
     a.part = m->attn_split; a.part_capacity = m->attn_split_floats; a.max_keys = d.window > 0 ? std::min(d.window, c.n_ctx) : c.n_ctx;
     {
         StepProfiler sp(m, st, 2);

@@ -308,6 +308,7 @@ struct SinkAttnArgs {
     float* cross;                                              // scratch [T][H][G][dv] (talk only)
     float* part; int part_capacity;                            // few-token steps: (max, sum, output) per key range, floats available
     int max_keys;                                              // most keys a query can see (the window, or the context size)
+    float* pbuf; size_t pbuf_floats;                           // prompts with mixed heads: the normalised weights of a group of query tiles
     float* out; int ld_out;                                    // out[t][h*dv + i]
 };
 // rotation (and unit RMS) of q and k, keys and values into the pages

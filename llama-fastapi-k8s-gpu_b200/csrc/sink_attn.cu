@@ -425,6 +425,281 @@ __global__ void __launch_bounds__(128) sink_attn_mma_kernel(SinkAttnArgs a, Ragg
         }
 }
 
+// ---- prompts with mixed heads (bf16 pages): the weights are mixed BEFORE they meet the values, in three passes over a group of
+// query tiles whose normalised weights fit the scratch `pbuf` ([tile][head][64 rows][span] f32, span = the most key blocks a tile
+// can touch x 64):
+//   1. sink_attn_probs_kernel  per (tile, head): scores twice -- first the running maximum and the sum (with the sink), then the
+//                              normalised weights exp(s - m) / l into pbuf (zeros where the mask hides a key)
+//   2. sink_attn_mix_kernel    per (tile, row): w_h <- sum_g talk[h][g] w_g in place, a chunk of columns at a time through shared memory
+//   3. sink_attn_pv_kernel     per (tile, head): O = W_h V with the values of the head's own key/value head, gate, store
+// Against the form that keeps a separate weighted sum per (query head, value head) pair this does the score products twice and
+// the value products once instead of G times each; the scratch costs two passes over HBM.
+struct SinkMix { int tile0, span; };
+
+template <int DMAX>
+__global__ void __launch_bounds__(128) sink_attn_probs_kernel(SinkAttnArgs a, RaggedDev r, SinkMix mx) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ __align__(16) unsigned char sk_smem[];
+    const int d = a.d, LD = d + 8;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(sk_smem);     // [64][LD] leading bf16 of the (scaled) query
+    __nv_bfloat16* Ql = Qs + SKM_Q * LD;                                // [64][LD] remainder
+    __nv_bfloat16* Ks = Ql + SKM_Q * LD;                                // [64][LD]
+    const int tile = mx.tile0 + blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = r.tile_seg[tile], row0 = r.tile_row0[tile];
+    const int nq = min(SKM_Q, r.seg_start[seg] + r.seg_len[seg] - row0);
+    const int p0 = r.tok_pos[row0], p_last = p0 + nq - 1;
+    const int* table = a.block_tables[r.seg_slot[seg]];
+    const int g = h / (a.H / a.G);
+    const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(a.k_pool);
+    for (int i = threadIdx.x; i < SKM_Q * (d / 2); i += blockDim.x) {
+        const int rr = i / (d / 2), c = (i % (d / 2)) * 2;
+        float2 v = make_float2(0.f, 0.f);
+        if (rr < nq) v = *reinterpret_cast<const float2*>(a.q_rot + ((size_t)(row0 + rr) * a.H + h) * d + c);
+        v.x *= a.scale; v.y *= a.scale;
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(v.x, v.y);
+        *reinterpret_cast<__nv_bfloat162*>(Qs + rr * LD + c) = hi;
+        *reinterpret_cast<__nv_bfloat162*>(Ql + rr * LD + c) = __floats2bfloat162_rn(v.x - __low2float(hi), v.y - __high2float(hi));
+    }
+    const int lo_first = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
+    const int b0 = lo_first / SKM_K, b1 = min(p_last / SKM_K, b0 + mx.span / SKM_K - 1);
+    const int gq = lane >> 2, tq = lane & 3;
+    const int qrow[2] = {warp * 16 + gq, warp * 16 + gq + 8};
+    int qlo[2];
+    float m_run[2], l_run[2], inv[2] = {0.f, 0.f};
+    const float sink = a.sink ? a.sink[h] : -INFINITY;
+#pragma unroll
+    for (int q2 = 0; q2 < 2; q2++) {
+        const int i = p0 + qrow[q2];
+        qlo[q2] = a.window > 0 ? max(0, i - a.window + 1) : 0;
+        m_run[q2] = sink; l_run[q2] = 0.f;
+    }
+    float* prow[2];
+#pragma unroll
+    for (int q2 = 0; q2 < 2; q2++) prow[q2] = a.pbuf + (((size_t)blockIdx.x * a.H + h) * SKM_Q + qrow[q2]) * mx.span;
+    for (int pass = 0; pass < 2; pass++) {
+        for (int kb = b0; kb <= b1; kb++) {
+            const int j0 = kb * SKM_K;
+            __syncthreads();                      // everybody is done with the previous block's K (and Q is written)
+            for (int i = threadIdx.x; i < SKM_K * (d / 8); i += blockDim.x) {
+                const int rr = i / (d / 8), c = (i % (d / 8)) * 8;
+                const int j = j0 + rr, jj = min(j, p_last);
+                const size_t base = (((size_t)table[jj / a.block_tokens] * a.G + g) * a.block_tokens + jj % a.block_tokens) * d + c;
+                sk_cp_async_16z(Ks + rr * LD + c, kp + base, j <= p_last ? 16 : 0);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+            float sacc[SKM_K / 8][4];
+#pragma unroll
+            for (int ni = 0; ni < SKM_K / 8; ni++) sacc[ni][0] = sacc[ni][1] = sacc[ni][2] = sacc[ni][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < DMAX; ks += 16) {
+                if (ks < d) {
+                    uint32_t af[4], al[4];
+                    sk_ldsm_x4(af, Qs + (warp * 16 + (lane & 15)) * LD + ks + (lane >> 4) * 8);
+                    sk_ldsm_x4(al, Ql + (warp * 16 + (lane & 15)) * LD + ks + (lane >> 4) * 8);
+#pragma unroll
+                    for (int nj = 0; nj < SKM_K / 16; nj++) {
+                        uint32_t bf[4];
+                        sk_ldsm_x4(bf, Ks + (nj * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + ks + ((lane >> 3) & 1) * 8);
+                        sk_mma_16816(sacc[2 * nj], al, bf[0], bf[1]);
+                        sk_mma_16816(sacc[2 * nj + 1], al, bf[2], bf[3]);
+                        sk_mma_16816(sacc[2 * nj], af, bf[0], bf[1]);
+                        sk_mma_16816(sacc[2 * nj + 1], af, bf[2], bf[3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int ni = 0; ni < SKM_K / 8; ni++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int rr = qrow[e >> 1], i = p0 + rr, j = j0 + ni * 8 + 2 * tq + (e & 1);
+                    const bool vis = rr < nq && j <= i && j >= qlo[e >> 1];
+                    sacc[ni][e] = vis ? sacc[ni][e] : -INFINITY;
+                }
+            if (pass == 0) {
+                float mxr[2] = {m_run[0], m_run[1]}, rs[2] = {0.f, 0.f}, msafe[2];
+#pragma unroll
+                for (int ni = 0; ni < SKM_K / 8; ni++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) mxr[e >> 1] = fmaxf(mxr[e >> 1], sacc[ni][e]);
+#pragma unroll
+                for (int q2 = 0; q2 < 2; q2++) {
+                    mxr[q2] = fmaxf(mxr[q2], __shfl_xor_sync(0xffffffffu, mxr[q2], 1));
+                    mxr[q2] = fmaxf(mxr[q2], __shfl_xor_sync(0xffffffffu, mxr[q2], 2));
+                    msafe[q2] = mxr[q2] > -INFINITY ? mxr[q2] : 0.f;
+                }
+#pragma unroll
+                for (int ni = 0; ni < SKM_K / 8; ni++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) rs[e >> 1] += __expf(sacc[ni][e] - msafe[e >> 1]);
+#pragma unroll
+                for (int q2 = 0; q2 < 2; q2++) {
+                    rs[q2] += __shfl_xor_sync(0xffffffffu, rs[q2], 1);
+                    rs[q2] += __shfl_xor_sync(0xffffffffu, rs[q2], 2);
+                    l_run[q2] = fmaf(l_run[q2], __expf(m_run[q2] - msafe[q2]), rs[q2]);
+                    m_run[q2] = mxr[q2];
+                }
+            } else {
+#pragma unroll
+                for (int ni = 0; ni < SKM_K / 8; ni++)
+#pragma unroll
+                    for (int q2 = 0; q2 < 2; q2++) {
+                        const float2 w = make_float2(__expf(sacc[ni][2 * q2] - m_run[q2]) * inv[q2], __expf(sacc[ni][2 * q2 + 1] - m_run[q2]) * inv[q2]);
+                        *reinterpret_cast<float2*>(prow[q2] + (kb - b0) * SKM_K + ni * 8 + 2 * tq) = w;
+                    }
+            }
+        }
+        if (pass == 0) {
+#pragma unroll
+            for (int q2 = 0; q2 < 2; q2++) {
+                const float msafe = m_run[q2] > -INFINITY ? m_run[q2] : 0.f;
+                const float l = l_run[q2] + (a.sink ? __expf(sink - msafe) : 0.f);
+                inv[q2] = l > 0.f ? 1.f / l : 0.f;
+                m_run[q2] = msafe;
+            }
+        }
+    }
+}
+
+// grid (tiles of the group * 64 rows), 256 threads; shared: talk [H][H], then [H][256] weights of a chunk of columns
+__global__ void __launch_bounds__(256) sink_attn_mix_kernel(SinkAttnArgs a, RaggedDev r, SinkMix mx) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ float mix_sm[];
+    const int H = a.H;
+    float* tk = mix_sm;
+    float* vals = mix_sm + H * H;
+    const int tl = blockIdx.x / SKM_Q, row = blockIdx.x % SKM_Q, tile = mx.tile0 + tl;
+    const int seg = r.tile_seg[tile], row0 = r.tile_row0[tile];
+    const int nq = min(SKM_Q, r.seg_start[seg] + r.seg_len[seg] - row0);
+    if (row >= nq) return;
+    const int p0 = r.tok_pos[row0], p_last = p0 + nq - 1;
+    const int lo_first = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
+    const int b0 = lo_first / SKM_K, b1 = min(p_last / SKM_K, b0 + mx.span / SKM_K - 1);
+    const int ncol = (b1 - b0 + 1) * SKM_K;
+    for (int i = threadIdx.x; i < H * H; i += blockDim.x) tk[i] = a.talk[i];
+    float* base = a.pbuf + ((size_t)tl * H * SKM_Q + row) * mx.span;          // head g adds g * 64 * span
+    const size_t hs = (size_t)SKM_Q * mx.span;
+    for (int c0 = 0; c0 < ncol; c0 += 256) {
+        const int c = c0 + threadIdx.x;
+        __syncthreads();
+        if (c < ncol) for (int g = 0; g < H; g++) vals[g * 256 + threadIdx.x] = base[g * hs + c];
+        __syncthreads();                           // also: talk is in place
+        if (c < ncol)
+            for (int h = 0; h < H; h++) {
+                float o = 0.f;
+                for (int g = 0; g < H; g++) o = fmaf(tk[h * H + g], vals[g * 256 + threadIdx.x], o);
+                base[h * hs + c] = o;
+            }
+    }
+}
+
+template <int DVMAX>
+__global__ void __launch_bounds__(128) sink_attn_pv_kernel(SinkAttnArgs a, RaggedDev r, SinkMix mx) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ __align__(16) unsigned char sk_smem[];
+    const int dv = a.dv, LDV = dv + 8;
+    __nv_bfloat16* Vs = reinterpret_cast<__nv_bfloat16*>(sk_smem);     // [64][LDV]
+    const int tile = mx.tile0 + blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = r.tile_seg[tile], row0 = r.tile_row0[tile];
+    const int nq = min(SKM_Q, r.seg_start[seg] + r.seg_len[seg] - row0);
+    const int p0 = r.tok_pos[row0], p_last = p0 + nq - 1;
+    const int* table = a.block_tables[r.seg_slot[seg]];
+    const int vg = h / (a.H / a.G);
+    const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(a.v_pool);
+    const int lo_first = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
+    const int b0 = lo_first / SKM_K, b1 = min(p_last / SKM_K, b0 + mx.span / SKM_K - 1);
+    const int gq = lane >> 2, tq = lane & 3;
+    const int qrow[2] = {warp * 16 + gq, warp * 16 + gq + 8};
+    const float* prow[2];
+#pragma unroll
+    for (int q2 = 0; q2 < 2; q2++) prow[q2] = a.pbuf + (((size_t)blockIdx.x * a.H + h) * SKM_Q + qrow[q2]) * mx.span;
+    float o[DVMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DVMAX / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int kb = b0; kb <= b1; kb++) {
+        const int j0 = kb * SKM_K;
+        __syncthreads();
+        for (int i = threadIdx.x; i < SKM_K * (dv / 8); i += blockDim.x) {
+            const int rr = i / (dv / 8), c = (i % (dv / 8)) * 8;
+            const int j = j0 + rr, jj = min(j, p_last);
+            const size_t base = (((size_t)table[jj / a.block_tokens] * a.G + vg) * a.block_tokens + jj % a.block_tokens) * dv + c;
+            sk_cp_async_16z(Vs + rr * LDV + c, vp + base, j <= p_last ? 16 : 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        // this block's mixed weights straight from the scratch in the MMA's row layout, while the values arrive
+        float2 w[SKM_K / 16][4];
+#pragma unroll
+        for (int kc = 0; kc < SKM_K / 16; kc++)
+#pragma unroll
+            for (int f = 0; f < 4; f++) {
+                const int rr = qrow[f & 1];
+                w[kc][f] = rr < nq ? *reinterpret_cast<const float2*>(prow[f & 1] + (kb - b0) * SKM_K + kc * 16 + (f >> 1) * 8 + 2 * tq) : make_float2(0.f, 0.f);
+            }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+#pragma unroll
+        for (int kc = 0; kc < SKM_K / 16; kc++) {
+            uint32_t pf[4], pl[4];
+#pragma unroll
+            for (int f = 0; f < 4; f++) sk_split_bf16(w[kc][f].x, w[kc][f].y, pf[f], pl[f]);
+#pragma unroll
+            for (int nd = 0; nd < DVMAX / 16; nd++) {
+                if (nd * 16 < dv) {
+                    uint32_t vf[4];
+                    sk_ldsm_x4_t(vf, Vs + (kc * 16 + (lane & 15)) * LDV + nd * 16 + (lane >> 4) * 8);
+                    sk_mma_16816(o[2 * nd], pl, vf[0], vf[1]);
+                    sk_mma_16816(o[2 * nd + 1], pl, vf[2], vf[3]);
+                    sk_mma_16816(o[2 * nd], pf, vf[0], vf[1]);
+                    sk_mma_16816(o[2 * nd + 1], pf, vf[2], vf[3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DVMAX / 8; i++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int rr = qrow[e >> 1], c = i * 8 + 2 * tq + (e & 1);
+            if (rr >= nq || c >= dv) continue;
+            const int t = row0 + rr;
+            a.out[(size_t)t * a.ld_out + (size_t)h * dv + c] = o[i][e] * sk_gate(a, t, h, c);
+        }
+}
+
+template <int DMAX>
+static cudaError_t sink_attn_probs_pick(const SinkAttnArgs& a, const RaggedDev& r, const SinkMix& mx, int nt, cudaStream_t s) {
+    static bool attr_done = false;
+    if (!attr_done) { cudaFuncSetAttribute(sink_attn_probs_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 64 * (DMAX + 8) * 2); attr_done = true; }
+    return launch_chain(sink_attn_probs_kernel<DMAX>, dim3(nt, a.H), dim3(128), (size_t)3 * 64 * (a.d + 8) * 2, s, a, r, mx);
+}
+template <int DVMAX>
+static cudaError_t sink_attn_pv_pick(const SinkAttnArgs& a, const RaggedDev& r, const SinkMix& mx, int nt, cudaStream_t s) {
+    return launch_chain(sink_attn_pv_kernel<DVMAX>, dim3(nt, a.H), dim3(128), (size_t)64 * (a.dv + 8) * 2, s, a, r, mx);
+}
+// false: the scratch cannot hold even one tile (or too many heads for the mixing pass's shared memory)
+static bool sink_attn_mixed_launch(const SinkAttnArgs& a, const RaggedDev& r, cudaStream_t s, cudaError_t& e) {
+    const int span = ((a.max_keys + 62) / 64 + 2) * 64;
+    const size_t per_tile = (size_t)a.H * SKM_Q * span;
+    const size_t mix_smem = (size_t)(a.H * a.H + a.H * 256) * 4;
+    if (!a.pbuf || per_tile > a.pbuf_floats || mix_smem > 96 * 1024) return false;
+    static bool attr_done = false;
+    if (!attr_done) { cudaFuncSetAttribute(sink_attn_mix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); attr_done = true; }
+    const int group = (int)std::min<size_t>(a.pbuf_floats / per_tile, (size_t)r.n_tiles);
+    e = cudaSuccess;
+    for (int t0 = 0; t0 < r.n_tiles && e == cudaSuccess; t0 += group) {
+        const int nt = std::min(group, r.n_tiles - t0);
+        SinkMix mx = {t0, span};
+        e = a.d <= 64 ? sink_attn_probs_pick<64>(a, r, mx, nt, s) : sink_attn_probs_pick<128>(a, r, mx, nt, s);
+        if (e == cudaSuccess) e = launch_chain(sink_attn_mix_kernel, dim3(nt * SKM_Q), dim3(256), mix_smem, s, a, r, mx);
+        if (e == cudaSuccess) e = a.dv <= 64 ? sink_attn_pv_pick<64>(a, r, mx, nt, s) : sink_attn_pv_pick<128>(a, r, mx, nt, s);
+    }
+    return true;
+}
+
 template <int DMAX, int DVMAX>
 static cudaError_t sink_attn_mma_pick(const SinkAttnArgs& a, const RaggedDev& r, cudaStream_t s) {
     const size_t smem = (size_t)(3 * 64 * (a.d + 8) + 64 * (a.dv + 8)) * 2;
@@ -442,6 +717,10 @@ cudaError_t sink_attn_launch(const SinkAttnArgs& a, const RaggedDev& r, cudaStre
     const int Gv = a.talk ? a.G : 1;
     cudaError_t e;
     if (!no_mma && !a.cache_f32 && r.T > SK_FEW_TOKENS && a.d % 16 == 0 && a.dv % 16 == 0 && a.d <= 128 && a.dv <= 128) {
+        static const bool no_mixed = getenv("B2_NO_ATTN_MIXED") != nullptr;    // tuning aid: one weighted sum per (query head, value head) pair
+        // with one or two key/value heads the separate sums cost no more than the second score pass and the scratch traffic
+        // (measured at 8 heads over 2: 0.84 against 1.08 ms for four layers and 2048 tokens)
+        if (a.talk && a.G >= 3 && !no_mixed && sink_attn_mixed_launch(a, r, s, e)) return e;
         if (a.d <= 64) e = a.dv <= 64 ? sink_attn_mma_pick<64, 64>(a, r, s) : sink_attn_mma_pick<64, 128>(a, r, s);
         else e = a.dv <= 64 ? sink_attn_mma_pick<128, 64>(a, r, s) : sink_attn_mma_pick<128, 128>(a, r, s);
     } else {

@@ -331,12 +331,14 @@ def test_far_token_through_the_state(native_lib, tmp_path):
 @pytest.mark.parametrize("window", [16, 64, 100, 0])
 def test_prompt_tiles(native_lib, tmp_path, window, dtype):
     """Sizes the tensor-core prompt kernels take: windows narrower and wider than the 64-query tile and none at all, key and
-    value sizes that are multiples of 16, enough (token, expert) pairs for 128-row expert tiles; a 300-token prompt at once and
-    in portions that straddle the tiles."""
+    value sizes that are multiples of 16, mixed heads over two key/value heads (one weighted sum per pair of query head and
+    value head) and over four (weights mixed before the values, through the scratch), enough (token, expert) pairs for 128-row
+    expert tiles; a 300-token prompt at once and in portions that straddle the tiles."""
     from llama_cpp.kv_pages import SequenceSlots
     cfg = nu.config([nu.parallel(mlp=nu.moe(experts=6, top=4, ff=16), left=nu.attn(heads=4, kv_heads=2, dim=32, vdim=16, window=window, rot=16)),
                      nu.attention(mlp=nu.dense(64), m=nu.attn(heads=2, kv_heads=2, dim=48, vdim=64, window=window, rot=8)),
-                     nu.parallel(left=nu.attn(heads=8, kv_heads=1, dim=64, vdim=80, window=window, rot=64), right=nu.delta(heads=2, kv_heads=2, dim=32, vdim=32))], width=64)
+                     nu.parallel(left=nu.attn(heads=8, kv_heads=4, dim=64, vdim=80, window=window, rot=64), right=nu.delta(heads=2, kv_heads=2, dim=32, vdim=32)),
+                     nu.parallel(left=nu.attn(heads=3, kv_heads=3, dim=16, vdim=128, window=window, rot=2))], width=64)
     w = nu.random_weights(cfg, seed=13)
     eng = open_engine(nu.write_model(str(tmp_path / "m"), cfg, w), dtype)
     toks = tokens_for(cfg, 300, 14)
