@@ -168,13 +168,13 @@ int b2_synchronize(b2_engine* e);
 #define B2_ROUTE_TOPK_SOFTMAX 1  /* biased logits choose; weights = softmax over the chosen logits */
 #define B2_BLOCK_POSTSUM_LN 0    /* x <- LayerNorm(alpha * x + f(x)) */
 #define B2_BLOCK_PRENORM_RMS 1   /* x <- x + m * f(RMSNorm(x) * (1 + w)); the embedding and the output are normed the same way */
+#define B2_BLOCK_OUTNORM_RMS 2   /* x <- x + RMSNorm_parts(f(x)) * w: the branch OUTPUT is normed, over norm_groups equal parts;
+                                    the output norm has the same form */
 #define B2_BLOCK_HYPER_RMS 3     /* n_streams copies x_1..x_S of the stream (all the embedding at first). A sublayer reads
                                     h = RMSNorm(sum_s in[s] x_s) * w, passed through a causal convolution with a skip when canon_taps > 0
                                     (h + conv(h), tensors l<i>.canon1/2 [W][taps]); its output y goes back as
                                     x_t <- sum_s mix[s][t] x_s + out[t] y (tensors l<i>.hc1/2.in, .mix, .out; absent: plain residual).
                                     The output norm reads the sum of the copies. */
-#define B2_BLOCK_OUTNORM_RMS 2   /* x <- x + RMSNorm_parts(f(x)) * w: the branch OUTPUT is normed, over norm_groups equal parts;
-                                    the output norm has the same form */
 typedef struct b2_layer_desc {
     int32_t mixer;            /* B2_MIX_* */
     int32_t n_ff;             /* width of the feed-forward block (of one expert for B2_FF_MOE); 0 = the layer has none */

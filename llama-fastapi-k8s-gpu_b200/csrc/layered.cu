@@ -1,11 +1,14 @@
 // Layer-list models (include/b200_gguf.h: b2_engine_create_layered, b2_step): the graph of a decoder given as a list of
 // layers over dense bf16 / f32 tensors, stepped over ragged batches. Token mixers: window attention beside a selective
 // scan, an mLSTM matrix memory, latent attention, the gated delta rule, a Mamba-2 state-space layer, chunk-local sigmoid
-// attention beside fixed-decay linear attention. Feed-forward blocks: squared ReLU with biases, a gated SiLU unit, or a routed
-// mixture of gated experts (with an optional shared expert). Three block styles: layer norm AFTER each residual sum,
-// pre-norm (zero-centred RMS weights) with a scaled branch, or an RMS norm in parts on each branch's OUTPUT. Shares the engine object with the llama graph (engine.cu): tensors, sequence slots and their page tables,
-// sampler state, stream, error reporting. Owns: fused projection matrices, per-layer cache pages, per-slot recurrent
-// state, the step workspace.
+// attention beside fixed-decay linear attention, softmax attention with a sink alone or beside a head-decay delta rule.
+// Feed-forward blocks: squared ReLU with biases, a gated SiLU unit, a block with a piecewise activation, or a routed mixture of
+// gated experts (SiLU or clamped; with an optional shared expert). Four block styles: layer norm AFTER each residual sum,
+// pre-norm (zero-centred RMS weights) with a scaled branch, an RMS norm in parts on each branch's OUTPUT, or pre-norm over
+// several copies of the stream with mixing matrices and a convolution on every sublayer's input. A layer entry may name another
+// layer's tensors (a repeated run of layers: shared weights, cache and state of its own). Shares the engine object with the
+// llama graph (engine.cu): tensors, sequence slots and their page tables, sampler state, stream, error reporting. Owns: fused
+// projection matrices, per-layer cache pages, per-slot recurrent state, the step workspace.
 #include "engine_state.h"
 #include "layered.h"
 #include "ptx.cuh"
